@@ -12,6 +12,7 @@ import os
 
 from .goguvik import GoguvikConfig
 from .kesedra import KesedraConfig
+from .korurax import KoruraxConfig
 from .qwen3 import ConfigError, Qwen3Config
 
 ARCHITECTURES: dict = {}
@@ -27,6 +28,7 @@ def register_architecture(name: str, config_cls) -> None:
 register_architecture(Qwen3Config.architecture, Qwen3Config)
 register_architecture(GoguvikConfig.architecture, GoguvikConfig)
 register_architecture(KesedraConfig.architecture, KesedraConfig)
+register_architecture(KoruraxConfig.architecture, KoruraxConfig)
 
 
 def architecture_name(raw: dict):

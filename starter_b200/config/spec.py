@@ -28,6 +28,15 @@ class NormSpec:
 
 
 @dataclass(frozen=True)
+class LayerNormSpec:
+    """Layer norm with a gain and no bias: ``(x - mean) / sqrt(mean((x - mean)^2) + eps) * gain``."""
+
+    size: int
+    eps: float
+    kind: str = "layernorm"
+
+
+@dataclass(frozen=True)
 class DynamicTanhSpec:
     """Dynamic Tanh in a norm's place: ``tanh(alpha * x) * weight + bias`` with a scalar ``alpha``; it
     takes no statistics of the row."""
@@ -53,6 +62,16 @@ class InterleavedRopeSpec:
     dims: int
     base: float
     kind: str = "rope_interleaved"
+
+
+@dataclass(frozen=True)
+class PartialRopeSpec:
+    """Rotary positions that turn entry ``i`` with entry ``i + dims / 2`` of the first ``dims`` entries of a
+    vector by the angle ``position * base ** (-2i / dims)``; entries from ``dims`` on pass unchanged."""
+
+    dims: int
+    base: float
+    kind: str = "rope_partial"
 
 
 @dataclass(frozen=True)
@@ -115,6 +134,34 @@ class DifferentialAttentionSpec:
 
 
 @dataclass(frozen=True)
+class SinkAttentionSpec:
+    """Causal grouped-query attention without rotation, whose positions enter through the scores and the
+    mask.  Each of the four is optional:
+
+    ``distance_penalty``: ``r1_h * ln(1 + r2_h * (i - j))`` is taken off the scaled score of query ``i`` and
+    key ``j`` (two learnt numbers per head).  ``chunk``: a query sees only the keys of its own chunk of
+    that many positions, chunks counted from position 0 of the sequence; ``window``: only the most recent
+    that many keys, its own included.  ``sink``: the softmax's denominator holds one more term
+    ``exp(sink_h)`` (a learnt number per head) that has no value.  ``head_gate``: a head's output is
+    multiplied by ``sigmoid(g_h . x)``, one learnt vector per head, read from the mixer's own input.
+    Keys have ``head_dim`` entries, values ``value_dim``."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    distance_penalty: bool = True
+    sink: bool = True
+    head_gate: bool = True
+    chunk: Optional[int] = None
+    window: Optional[int] = None
+    position: Optional[object] = None
+    kind: str = "sink_attention"
+
+
+@dataclass(frozen=True)
 class LatentAttentionSpec:
     """Causal attention whose keys and values are up-projections of one cached low-rank latent per token.
 
@@ -135,7 +182,9 @@ class LatentAttentionSpec:
     kv_rank: int
     scale: float
     norm_eps: float
-    position: Optional[InterleavedRopeSpec]
+    #: how the rotated parts turn: ``InterleavedRopeSpec`` (entry 2i with 2i + 1) or ``PartialRopeSpec``
+    #: (entry i with i + dims / 2)
+    position: Optional[object]
     window: Optional[int] = None
     own_kv: bool = True
     kind: str = "latent_attention"
@@ -171,17 +220,48 @@ class BiasedFeedForwardSpec:
 
 @dataclass(frozen=True)
 class RoutedExpertsSpec:
-    """A mixture of ``experts`` small gated feed-forwards without biases, of which a token uses the ``top``
-    with the largest router logits (``router(x) + bias`` in 32-bit), weighted by the softmax over those
-    logits alone.  An expert: ``down(g * sigmoid(1.702 g) * (u + 1))`` with ``g = min(gate(x), limit)``,
-    ``u = clamp(up(x), -limit, limit)``."""
+    """A mixture of ``experts`` small feed-forwards without biases, of which a token uses the ``top`` with
+    the largest router logits (``router(x)``, plus a bias when ``router_bias``, in 32-bit).
+
+    ``scoring`` ``"softmax_top"``: the weights are the softmax over the chosen logits alone;
+    ``"sigmoid_normalised"``: the chosen experts' ``sigmoid(logit)`` divided by their sum (+ 1e-20), times
+    ``weight_scale``.  ``expert`` ``"gated_clamped"``: ``down(g * sigmoid(1.702 g) * (u + 1))`` with ``g =
+    min(gate(x), limit)``, ``u = clamp(up(x), -limit, limit)``; ``"relu2"``: ``down(relu(up(x))^2)``, no gate
+    and no limit."""
 
     hidden_size: int
     intermediate_size: int
     experts: int
     top: int
-    limit: float
+    limit: float = 0.0
+    expert: str = "gated_clamped"
+    scoring: str = "softmax_top"
+    weight_scale: float = 1.0
+    router_bias: bool = True
     kind: str = "routed_experts"
+
+
+@dataclass(frozen=True)
+class ClampedGatedFeedForwardSpec:
+    """Dense gated feed-forward with clamps: ``down(g * sigmoid(1.702 g) * (u + 1))`` with ``g = min(gate(x),
+    limit)`` and ``u = clamp(up(x), -limit, limit)``; no biases."""
+
+    hidden_size: int
+    intermediate_size: int
+    limit: float
+    kind: str = "gated_clamped"
+
+
+@dataclass(frozen=True)
+class DepthAverageSpec:
+    """How a layer stands in a float32 residual stream that is joined over depth: its sublayers' outputs
+    enter the stream times ``multiplier``, and behind the layer the stream becomes the weighted sum of the
+    embedding output and of all ``levels - 1`` layer results so far (``levels`` learnt weights, the
+    embedding's first)."""
+
+    levels: int
+    multiplier: float = 1.0
+    kind: str = "depth_average"
 
 
 @dataclass(frozen=True)
@@ -245,6 +325,15 @@ def sandwich_layer(mixer, feed_forward, norm, names) -> LayerSpec:
                       "norm2": norm, "norm2b": norm}, names, "sandwich")
 
 
+def depth_layer(mixer, feed_forward, norm1, norm2, connection, names) -> LayerSpec:
+    """A pre-norm layer in a stream joined over depth (see ``DepthAverageSpec``); ``feed_forward`` (and
+    ``norm2``) None: the layer is its mixer alone."""
+    if feed_forward is None:
+        return LayerSpec({"mixer": mixer, "norm1": norm1, "connection": connection}, names, "depth_mixer_only")
+    return LayerSpec({"mixer": mixer, "feed_forward": feed_forward, "norm1": norm1, "norm2": norm2,
+                      "connection": connection}, names, "depth_prenorm")
+
+
 def prenorm_layer(mixer, feed_forward, norm1, norm2, names, arrangement: str = "prenorm") -> LayerSpec:
     """The layer of the pre-norm block: ``x + mixer(norm1(x))``, then ``+ feed_forward(norm2(.))``."""
     return LayerSpec({"mixer": mixer, "feed_forward": feed_forward, "norm1": norm1, "norm2": norm2},
@@ -292,6 +381,8 @@ class ModelSpec:
     ignored_tensors: tuple = ()
     #: what a token's embedding is multiplied by (models whose residual stream is float32)
     embedding_scale: float = 1.0
+    #: None, or the constant ``c`` of ``logits <- c * tanh(logits / c)``
+    logit_softcap: Optional[float] = None
 
     def cache_entries(self) -> int:
         return 1 + max((e.cache for e in self.schedule), default=-1)

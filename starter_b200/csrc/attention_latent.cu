@@ -15,8 +15,9 @@
 // RMS-normed (gain qg) into cq; the key/value latent is RMS-normed (gain kg) and filed in the cache
 // row of the token's position; the shared key part is turned by the token's position and filed behind
 // it.  latent_rotate_q turns the rotated part of every head's query and files it behind q'.
-// Rotation: pairs (2i, 2i + 1) of the first rot_dims entries, by the angle whose cos and sin the
-// tables hold at [position][i]; entries from rot_dims on pass unchanged.  Norms, angles, scores, the
+// Rotation: pairs (2i, 2i + 1) of the first rot_dims entries (`split` 0), or pairs (i, i + rot_dims / 2)
+// (`split` 1), by the angle whose cos and sin the tables hold at [position][i]; entries from rot_dims on
+// pass unchanged.  Norms, angles, scores, the
 // softmax and the sums over keys are float.
 #include "common.cuh"
 
@@ -26,7 +27,8 @@ __global__ void latent_prepare_kernel(const T* __restrict__ proj, int proj_width
                                       const float* __restrict__ sin_t, int table_width,
                                       const int* __restrict__ tok_pos, const int* __restrict__ tok_slot,
                                       const int* __restrict__ block_table, int table_stride, T* __restrict__ store,
-                                      T* __restrict__ cq, int q_rank, int rank, int rot, int rot_dims, int write) {
+                                      T* __restrict__ cq, int q_rank, int rank, int rot, int rot_dims, int write,
+                                      int split) {
   __shared__ float scratch[33];
   pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(proj);
@@ -61,10 +63,11 @@ __global__ void latent_prepare_kernel(const T* __restrict__ proj, int proj_width
   for (int c = threadIdx.x; c < rank; c += blockDim.x) dst[c] = from_f<T>(to_f<T>(kv[c]) * inv * kg[c]);
   const T* shared = kv + rank;
   for (int i = threadIdx.x; i < rot_dims / 2; i += blockDim.x) {
-    const float a = to_f<T>(shared[2 * i]), b = to_f<T>(shared[2 * i + 1]);
+    const int ia = split ? i : 2 * i, ib = split ? i + rot_dims / 2 : 2 * i + 1;
+    const float a = to_f<T>(shared[ia]), b = to_f<T>(shared[ib]);
     const float c = cos_t[(size_t)pos * table_width + i], s = sin_t[(size_t)pos * table_width + i];
-    dst[rank + 2 * i] = from_f<T>(a * c - b * s);
-    dst[rank + 2 * i + 1] = from_f<T>(b * c + a * s);
+    dst[rank + ia] = from_f<T>(a * c - b * s);
+    dst[rank + ib] = from_f<T>(b * c + a * s);
   }
   for (int c = rot_dims + threadIdx.x; c < rot; c += blockDim.x) dst[rank + c] = shared[c];
 }
@@ -75,7 +78,7 @@ template <typename T>
 __global__ void latent_rotate_q_kernel(const T* __restrict__ q, T* __restrict__ qa, const float* __restrict__ cos_t,
                                        const float* __restrict__ sin_t, int table_width,
                                        const int* __restrict__ tok_pos, int heads, int dim, int rot, int rot_dims,
-                                       int rank) {
+                                       int rank, int split) {
   pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(q);
   SB_BEHIND_WAIT(tok_pos);
@@ -88,10 +91,11 @@ __global__ void latent_rotate_q_kernel(const T* __restrict__ q, T* __restrict__ 
     const T* src = q + ((size_t)row * heads + h) * (dim + rot) + dim;
     T* dst = qa + ((size_t)row * heads + h) * (rank + rot) + rank;
     if (i < half) {
-      const float a = to_f<T>(src[2 * i]), b = to_f<T>(src[2 * i + 1]);
+      const int ia = split ? i : 2 * i, ib = split ? i + half : 2 * i + 1;
+      const float a = to_f<T>(src[ia]), b = to_f<T>(src[ib]);
       const float c = cos_t[(size_t)pos * table_width + i], s = sin_t[(size_t)pos * table_width + i];
-      dst[2 * i] = from_f<T>(a * c - b * s);
-      dst[2 * i + 1] = from_f<T>(b * c + a * s);
+      dst[ia] = from_f<T>(a * c - b * s);
+      dst[ib] = from_f<T>(b * c + a * s);
     } else {
       dst[rot_dims + i - half] = src[rot_dims + i - half];
     }
@@ -204,29 +208,29 @@ int sb_latent_max_row() { return 32 * 20; }
 int sb_latent_prepare(int dtype, const void* proj, int proj_width, const float* qg, const float* kg, float eps,
                       const float* cos_t, const float* sin_t, int table_width, const int* tok_pos,
                       const int* tok_slot, const int* block_table, int table_stride, void* store, void* cq,
-                      int n_tokens, int q_rank, int rank, int rot, int rot_dims, int write, cudaStream_t s) {
+                      int n_tokens, int q_rank, int rank, int rot, int rot_dims, int write, int split, cudaStream_t s) {
   if (n_tokens == 0) return 0;
   if (rot_dims % 2 || rot_dims > rot || rot_dims / 2 > table_width) return -2;
   if (proj_width < q_rank + (write ? rank + rot : 0)) return -2;
   if (dtype == 0)
     return launch_dependent(latent_prepare_kernel<float>, dim3(n_tokens), dim3(128), 0, s, (const float*)proj,
                             proj_width, qg, kg, eps, cos_t, sin_t, table_width, tok_pos, tok_slot, block_table,
-                            table_stride, (float*)store, (float*)cq, q_rank, rank, rot, rot_dims, write);
+                            table_stride, (float*)store, (float*)cq, q_rank, rank, rot, rot_dims, write, split);
   return launch_dependent(latent_prepare_kernel<bf16>, dim3(n_tokens), dim3(128), 0, s, (const bf16*)proj, proj_width,
                           qg, kg, eps, cos_t, sin_t, table_width, tok_pos, tok_slot, block_table, table_stride,
-                          (bf16*)store, (bf16*)cq, q_rank, rank, rot, rot_dims, write);
+                          (bf16*)store, (bf16*)cq, q_rank, rank, rot, rot_dims, write, split);
 }
 
 int sb_latent_rotate_q(int dtype, const void* q, void* qa, const float* cos_t, const float* sin_t, int table_width,
                        const int* tok_pos, int n_tokens, int heads, int dim, int rot, int rot_dims, int rank,
-                       cudaStream_t s) {
+                       int split, cudaStream_t s) {
   if (n_tokens == 0 || rot == 0) return 0;
   if (rot_dims % 2 || rot_dims > rot || rot_dims / 2 > table_width) return -2;
   if (dtype == 0)
     return launch_dependent(latent_rotate_q_kernel<float>, dim3(n_tokens), dim3(128), 0, s, (const float*)q,
-                            (float*)qa, cos_t, sin_t, table_width, tok_pos, heads, dim, rot, rot_dims, rank);
+                            (float*)qa, cos_t, sin_t, table_width, tok_pos, heads, dim, rot, rot_dims, rank, split);
   return launch_dependent(latent_rotate_q_kernel<bf16>, dim3(n_tokens), dim3(128), 0, s, (const bf16*)q, (bf16*)qa,
-                          cos_t, sin_t, table_width, tok_pos, heads, dim, rot, rot_dims, rank);
+                          cos_t, sin_t, table_width, tok_pos, heads, dim, rot, rot_dims, rank, split);
 }
 
 // qa: [n_tokens, heads, rank + rot]; out: [n_tokens, heads, rank]; store as above.

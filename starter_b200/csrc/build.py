@@ -53,6 +53,8 @@ SOURCES = (
     "wkv",
     "attention_latent",
     "moe",
+    "depth",
+    "attention_sink",
 )
 
 _lock = threading.Lock()

@@ -350,6 +350,24 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ act,
   }
 }
 
+// act[r, c] = g * sigmoid(1.702 g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit) for
+// gate = gu[r, c], up = gu[r, inner + c]: the clamped gated activation, in float.
+template <typename T>
+__global__ void gated_clamped_kernel(const T* __restrict__ gu, T* __restrict__ act, int inner, size_t total, float limit) {
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(gu);
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const size_t row = i / inner;
+    const int col = (int)(i - row * inner);
+    const float g = fminf(to_f<T>(gu[row * 2 * inner + col]), limit);
+    const float u = fminf(fmaxf(to_f<T>(gu[row * 2 * inner + inner + col]), -limit), limit);
+    act[i] = from_f<T>(g / (1.f + expf(-1.702f * g)) * (u + 1.f));
+  }
+}
+
 extern "C" {
 
 // dtype: 0 float, 1 bfloat16.  gain_dtype likewise.
@@ -399,6 +417,16 @@ int sb_swiglu(int dtype, const void* gu, void* act, int n_rows, int inner, int k
   if (dtype == 0)
     return launch_dependent(swiglu_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, (const float*)gu, (float*)act, inner, total, kind);
   return launch_dependent(swiglu_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, s, (const bf16*)gu, (bf16*)act, inner, total, kind);
+}
+
+int sb_gated_clamped(int dtype, const void* gu, void* act, int n_rows, int inner, float limit, cudaStream_t s) {
+  const size_t total = (size_t)n_rows * inner;
+  if (total == 0) return 0;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == 0)
+    return launch_dependent(gated_clamped_kernel<float>, dim3((int)blocks), dim3(256), 0, s, (const float*)gu, (float*)act, inner, total, limit);
+  return launch_dependent(gated_clamped_kernel<bf16>, dim3((int)blocks), dim3(256), 0, s, (const bf16*)gu, (bf16*)act, inner, total, limit);
 }
 
 }  // extern "C"

@@ -2,11 +2,13 @@
 // from the host between its kernels (so that it can sit inside a captured step).
 //
 //   route    z = W_r h + b in float; the `top` largest (the lower index first among equals); their
-//            weights are the softmax over those `top` logits alone.
+//            weights are the softmax over those `top` logits alone (scoring 0), or their sigmoids divided
+//            by the sum of those sigmoids (+ 1e-20) and multiplied by a constant (scoring 1).
 //   align    the (token, choice) pairs grouped by expert: every expert's pairs fill whole tiles of
 //            rows (32, or 64 for the tensor-core tiles; padded with -1), `tile_expert` names each tile's expert, `n_tiles` counts them.
 //   up       per tile: g = min(gate(h), limit), u = clamp(up(h), -limit, limit),
-//            a = g * sigmoid(1.702 g) * (u + 1), for the tile's rows gathered from h.
+//            a = g * sigmoid(1.702 g) * (u + 1), for the tile's rows gathered from h (expert kind 1);
+//            or, for experts without a gate, a = relu(up(h))^2 (expert kind 2).
 //   down     per tile: the expert's down projection of a, filed at the pair's own place.
 //   combine  out[t] = sum_c weight[t][c] * down[t][c], summed in float in the order of the choices.
 //
@@ -25,7 +27,8 @@
 
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w, const float* __restrict__ b,
-                                 int* __restrict__ ids, float* __restrict__ weights, int width, int experts, int top) {
+                                 int* __restrict__ ids, float* __restrict__ weights, int width, int experts, int top,
+                                 int scoring, float weight_scale) {
   extern __shared__ float z[];
   pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(h);
@@ -66,10 +69,14 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
     if (lane == 0) {
       float sum = 0.f;
       for (int c = 0; c < top; ++c) {
-        best[c] = expf(best[c] - top_max);
+        best[c] = scoring == 1 ? 1.f / (1.f + expf(-best[c])) : expf(best[c] - top_max);
         sum += best[c];
       }
-      for (int c = 0; c < top; ++c) weights[(size_t)row * top + c] = best[c] / sum;
+      if (scoring == 1) {
+        for (int c = 0; c < top; ++c) weights[(size_t)row * top + c] = best[c] / (sum + 1e-20f) * weight_scale;
+      } else {
+        for (int c = 0; c < top; ++c) weights[(size_t)row * top + c] = best[c] / sum;
+      }
     }
   }
 }
@@ -106,16 +113,18 @@ __global__ void moe_align_kernel(const int* __restrict__ ids, int n_pairs, int e
 }
 
 // A tile of MOE_BM rows times MOE_BN outputs in float on the CUDA cores: the 32-bit path, and the
-// working-type path for widths the tensor-core kernel does not take.  UP: rows gathered from h by
-// pair / top, two weight blocks (gate, up) and the activation; else rows of `a`, one block, results
-// filed by pair.
-template <typename T, bool UP>
+// working-type path for widths the tensor-core kernel does not take.  MODE 1: rows gathered from h by
+// pair / top, two weight blocks (gate, up) and the gated activation; MODE 2: rows gathered likewise, one
+// weight block, squared relu; MODE 0: rows of `a`, one block, results filed by pair.
+template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 moe_tile_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y, const int* __restrict__ sorted,
                 const int* __restrict__ tile_expert, const int* __restrict__ n_tiles, int k_dim, int n_out, int top,
                 float limit) {
   __shared__ float xs[MOE_BM][MOE_BK + 1];
-  __shared__ float ws[UP ? 2 : 1][MOE_BN][MOE_BK + 1];
+  constexpr bool UP = MODE != 0;
+  constexpr int NW = MODE == 1 ? 2 : 1;
+  __shared__ float ws[NW][MOE_BN][MOE_BK + 1];
   __shared__ int src[MOE_BM];
   // (launch_dependents comes at this kernel's end, not its start: it runs in several waves of large blocks,
   // and a successor that starts early would only sit on the SMs its later waves need)
@@ -131,11 +140,11 @@ moe_tile_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict_
   const int tid = threadIdx.x;
   if (tid < MOE_BM) src[tid] = sorted[tile * MOE_BM + tid];
   __syncthreads();
-  const T* we = w + (size_t)e * (UP ? 2 : 1) * n_out * k_dim;
+  const T* we = w + (size_t)e * NW * n_out * k_dim;
   const int ty = tid >> 4, tx = tid & 15;
-  float acc[UP ? 2 : 1][2][4];
+  float acc[NW][2][4];
 #pragma unroll
-  for (int a = 0; a < (UP ? 2 : 1); ++a)
+  for (int a = 0; a < NW; ++a)
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -151,7 +160,7 @@ moe_tile_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict_
       }
       xs[m][kk] = v;
     }
-    for (int i = tid; i < (UP ? 2 : 1) * MOE_BN * MOE_BK; i += 256) {
+    for (int i = tid; i < NW * MOE_BN * MOE_BK; i += 256) {
       const int a = i / (MOE_BN * MOE_BK), rem = i % (MOE_BN * MOE_BK);
       const int n = rem / MOE_BK, kk = rem % MOE_BK;
       float v = 0.f;
@@ -163,7 +172,7 @@ moe_tile_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict_
     for (int kk = 0; kk < MOE_BK; ++kk) {
       const float x0 = xs[ty * 2][kk], x1 = xs[ty * 2 + 1][kk];
 #pragma unroll
-      for (int a = 0; a < (UP ? 2 : 1); ++a)
+      for (int a = 0; a < NW; ++a)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float wv = ws[a][tx + 16 * j][kk];
@@ -181,12 +190,15 @@ moe_tile_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict_
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx + 16 * j;
       if (n >= n_out) continue;
-      if (UP) {
-        float g = rnd<T>(acc[0][i][j]), u = rnd<T>(acc[UP ? 1 : 0][i][j]);
+      if (MODE == 1) {
+        float g = rnd<T>(acc[0][i][j]), u = rnd<T>(acc[NW - 1][i][j]);
         g = fminf(g, limit);
         u = fminf(fmaxf(u, -limit), limit);
         const float a = pair >= 0 ? g / (1.f + expf(-1.702f * g)) * (u + 1.f) : 0.f;
         y[((size_t)tile * MOE_BM + m) * n_out + n] = from_f<T>(a);
+      } else if (MODE == 2) {
+        const float u = fmaxf(rnd<T>(acc[0][i][j]), 0.f);
+        y[((size_t)tile * MOE_BM + m) * n_out + n] = from_f<T>(pair >= 0 ? u * u : 0.f);
       } else if (pair >= 0) {
         y[(size_t)pair * n_out + n] = from_f<T>(acc[0][i][j]);
       }
@@ -205,13 +217,14 @@ __device__ __forceinline__ void moe_cp16(void* dst, const void* src, bool real) 
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
 }
 
-template <bool UP>
+template <int MODE>
 __global__ void __launch_bounds__(256)
 moe_tile_tc_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
                    const int* __restrict__ sorted, const int* __restrict__ tile_expert,
                    const int* __restrict__ n_tiles, int k_dim, int n_out, int top, float limit) {
   using namespace nvcuda;
-  constexpr int BK = 32, LD = BK + 8, NW = UP ? 2 : 1, STAGES = 3, CLD = MOE_BN + 4;
+  constexpr bool UP = MODE != 0;
+  constexpr int BK = 32, LD = BK + 8, NW = MODE == 1 ? 2 : 1, STAGES = 3, CLD = MOE_BN + 4;
   extern __shared__ __align__(128) unsigned char moe_smem[];
   bf16* xs = reinterpret_cast<bf16*>(moe_smem);                          // [STAGES][64][LD]
   bf16* ws = xs + STAGES * MOE_TC_BM * LD;                               // [STAGES][NW][64][LD]
@@ -293,12 +306,15 @@ moe_tile_tc_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
     const int n = n0 + nn;
     const int row_pair = src[m];
     if (n >= n_out) continue;
-    if (UP) {
+    if (MODE == 1) {
       float g = rnd<bf16>(cs[(size_t)m * CLD + nn]), u = rnd<bf16>(cs[((size_t)(NW - 1) * MOE_TC_BM + m) * CLD + nn]);
       g = fminf(g, limit);
       u = fminf(fmaxf(u, -limit), limit);
       const float a = row_pair >= 0 ? g / (1.f + expf(-1.702f * g)) * (u + 1.f) : 0.f;
       y[((size_t)tile * MOE_TC_BM + m) * n_out + n] = from_f<bf16>(a);
+    } else if (MODE == 2) {
+      const float u = fmaxf(rnd<bf16>(cs[(size_t)m * CLD + nn]), 0.f);
+      y[((size_t)tile * MOE_TC_BM + m) * n_out + n] = from_f<bf16>(row_pair >= 0 ? u * u : 0.f);
     } else if (row_pair >= 0) {
       y[(size_t)row_pair * n_out + n] = from_f<bf16>(cs[(size_t)m * CLD + nn]);
     }
@@ -320,6 +336,31 @@ __global__ void moe_combine_kernel(const T* __restrict__ down, const float* __re
   }
 }
 
+// up 1: x = h [n_tokens, k_dim], w = [experts, 2 * n_out, k_dim] (gate rows, then up rows), y =
+// [capacity, n_out] in the order of `sorted`, the clamped gated activation.  up 2: the same with w =
+// [experts, n_out, k_dim] and the squared relu.  up 0: x = that y [capacity, k_dim], w = [experts,
+// n_out, k_dim], y = [n_pairs, n_out] by pair.
+template <int MODE>
+static int moe_tiles_mode(int dtype, int tile_rows, const void* x, const void* w, void* y, const int* sorted,
+                          const int* tile_expert, const int* n_tiles, int max_tiles, int k_dim, int n_out, int top,
+                          float limit, cudaStream_t s) {
+  const dim3 grid(max_tiles, (n_out + MOE_BN - 1) / MOE_BN);
+  if (tile_rows == MOE_TC_BM) {
+    if (dtype != 1 || k_dim % 16 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16)) return -2;
+    constexpr int NW = MODE == 1 ? 2 : 1;
+    const size_t smem = (size_t)3 * (1 + NW) * 64 * 40 * sizeof(bf16) + (size_t)NW * 64 * (MOE_BN + 4) * sizeof(float);
+    cudaFuncSetAttribute(moe_tile_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_dependent(moe_tile_tc_kernel<MODE>, grid, dim3(256), smem, s, (const bf16*)x, (const bf16*)w,
+                            (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
+  }
+  if (tile_rows != MOE_BM) return -2;
+  if (dtype == 0)
+    return launch_dependent(moe_tile_kernel<float, MODE>, grid, dim3(256), 0, s, (const float*)x, (const float*)w,
+                            (float*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
+  return launch_dependent(moe_tile_kernel<bf16, MODE>, grid, dim3(256), 0, s, (const bf16*)x, (const bf16*)w,
+                          (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
+}
+
 extern "C" {
 
 // Rows of a tile for these operands: 64 when both products run on the tensor-core tiles (bfloat16, width and
@@ -332,16 +373,18 @@ int sb_moe_max_top() { return MOE_MAX_TOP; }
 
 // h: [n_tokens, width]; w: float [experts, width]; b: float [experts] or null; ids: int [n_tokens, top];
 // weights: float [n_tokens, top].
+// scoring 0: softmax over the chosen logits; 1: sigmoid scores divided by their sum, times weight_scale.
 int sb_moe_route(int dtype, const void* h, const float* w, const float* b, int* ids, float* weights, int n_tokens,
-                 int width, int experts, int top, cudaStream_t s) {
+                 int width, int experts, int top, int scoring, float weight_scale, cudaStream_t s) {
   if (n_tokens == 0) return 0;
   if (experts < 1 || experts > MOE_MAX_EXPERTS || top < 1 || top > MOE_MAX_TOP || top > experts) return -2;
+  if (scoring != 0 && scoring != 1) return -2;
   const size_t smem = (size_t)experts * sizeof(float);
   if (dtype == 0)
     return launch_dependent(moe_route_kernel<float>, dim3(n_tokens), dim3(128), smem, s, (const float*)h, w, b, ids,
-                            weights, width, experts, top);
+                            weights, width, experts, top, scoring, weight_scale);
   return launch_dependent(moe_route_kernel<bf16>, dim3(n_tokens), dim3(128), smem, s, (const bf16*)h, w, b, ids,
-                          weights, width, experts, top);
+                          weights, width, experts, top, scoring, weight_scale);
 }
 
 int sb_moe_align(const int* ids, int n_pairs, int experts, int* sorted, int capacity, int* tile_expert, int* n_tiles,
@@ -351,39 +394,16 @@ int sb_moe_align(const int* ids, int n_pairs, int experts, int* sorted, int capa
                           tile_expert, n_tiles, tile_rows);
 }
 
-// up != 0: x = h [n_tokens, k_dim], w = [experts, 2 * n_out, k_dim] (gate rows, then up rows), y =
-// [capacity, n_out] in the order of `sorted`.  up == 0: x = that y [capacity, k_dim], w = [experts,
-// n_out, k_dim], y = [n_pairs, n_out] by pair.
 int sb_moe_tiles(int dtype, int up, int tile_rows, const void* x, const void* w, void* y, const int* sorted,
                  const int* tile_expert, const int* n_tiles, int max_tiles, int k_dim, int n_out, int top, float limit,
                  cudaStream_t s) {
   if (max_tiles == 0) return 0;
-  const dim3 grid(max_tiles, (n_out + MOE_BN - 1) / MOE_BN);
-  if (tile_rows == MOE_TC_BM) {
-    if (dtype != 1 || k_dim % 16 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16)) return -2;
-    const size_t smem = (size_t)3 * (1 + (up ? 2 : 1)) * 64 * 40 * sizeof(bf16) + (size_t)(up ? 2 : 1) * 64 * (MOE_BN + 4) * sizeof(float);
-    if (up) {
-      cudaFuncSetAttribute(moe_tile_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      return launch_dependent(moe_tile_tc_kernel<true>, grid, dim3(256), smem, s, (const bf16*)x, (const bf16*)w,
-                              (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
-    }
-    cudaFuncSetAttribute(moe_tile_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch_dependent(moe_tile_tc_kernel<false>, grid, dim3(256), smem, s, (const bf16*)x, (const bf16*)w,
-                            (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
-  }
-  if (tile_rows != MOE_BM) return -2;
-  if (dtype == 0) {
-    if (up)
-      return launch_dependent(moe_tile_kernel<float, true>, grid, dim3(256), 0, s, (const float*)x, (const float*)w,
-                              (float*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
-    return launch_dependent(moe_tile_kernel<float, false>, grid, dim3(256), 0, s, (const float*)x, (const float*)w,
-                            (float*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
-  }
-  if (up)
-    return launch_dependent(moe_tile_kernel<bf16, true>, grid, dim3(256), 0, s, (const bf16*)x, (const bf16*)w,
-                            (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
-  return launch_dependent(moe_tile_kernel<bf16, false>, grid, dim3(256), 0, s, (const bf16*)x, (const bf16*)w,
-                          (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
+#define MOE_ARGS dtype, tile_rows, x, w, y, sorted, tile_expert, n_tiles, max_tiles, k_dim, n_out, top, limit, s
+  if (up == 0) return moe_tiles_mode<0>(MOE_ARGS);
+  if (up == 1) return moe_tiles_mode<1>(MOE_ARGS);
+  if (up == 2) return moe_tiles_mode<2>(MOE_ARGS);
+#undef MOE_ARGS
+  return -2;
 }
 
 int sb_moe_combine(int dtype, const void* down, const float* weights, void* out, int n_tokens, int width, int top,

@@ -13,6 +13,7 @@ import torch
 
 from .. import ops
 from ..parts import ParamSpec, lookup
+from ..parts.depth import close_rows_depth, open_stream
 from ..parts.hyper import close_rows
 from ..parts.sandwich import close_rows32
 
@@ -103,11 +104,15 @@ class DecoderModel:
         if not self.many_streams and spec.streams != 1:
             raise ValueError(f"the spec asks for {spec.streams} residual streams but its layers keep one")
         #: True when the layers keep the residual stream in float32 (norms on both sides of a sublayer)
-        kinds = {getattr(b, "residual_kind", None) == "float32" for b in self.blocks}
+        kinds = {getattr(b, "residual_kind", None) for b in self.blocks}
         if len(kinds) > 1:
-            raise ValueError("layers with a float32 residual stream and layers with one of the working type "
-                             "cannot be mixed")
-        self.float_residual = kinds == {True}
+            raise ValueError("layers with a float32 residual stream, layers with one joined over depth and layers "
+                             "with one of the working type cannot be mixed")
+        self.float_residual = kinds == {"float32"}
+        #: True when the layers keep a float32 residual stream that is joined over depth; the stream then
+        #: holds every layer's result, one level per run of a layer and one for the embedding
+        self.depth_residual = kinds == {"depth"}
+        self.depth_levels = max((b.levels for b in self.blocks), default=1) if self.depth_residual else 0
         if not self.float_residual and spec.embedding_scale != 1.0:
             raise ValueError("an embedding scale needs layers that keep a float32 residual stream")
         for entry in spec.schedule:
@@ -187,6 +192,8 @@ class DecoderModel:
             residual = ops.embedding_streams(ctx.tokens, self.embed, self.spec.streams, ctx.status, fence=True)
         elif self.float_residual:
             residual = ops.embedding32(ctx.tokens, self.embed, self.spec.embedding_scale, ctx.status, fence=True)
+        elif self.depth_residual:
+            residual = open_stream(ctx.tokens, self.embed, self.depth_levels, ctx.status)
         else:
             residual = ops.embedding(ctx.tokens, self.embed, ctx.status, fence=True)
         ctx.fenced = True
@@ -202,9 +209,14 @@ class DecoderModel:
             h = close_rows(residual, pending, rows, self.final_norm, self.dtype)
         elif self.float_residual:
             h = close_rows32(residual, pending, rows, self.final_norm, self.dtype)
+        elif self.depth_residual:
+            h = close_rows_depth(residual, pending, rows, self.final_norm, self.dtype)
         else:
             h = self.final_norm.add_rows(residual, pending, rows)
-        return ops.linear(h, self.lm_head, out_float=True, status=status)
+        logits = ops.linear(h, self.lm_head, out_float=True, status=status)
+        if self.spec.logit_softcap is not None:
+            ops.softcap(logits, self.spec.logit_softcap)
+        return logits
 
     def forward(self, ctx, rows):
         residual, pending = self.hidden(ctx)

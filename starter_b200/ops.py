@@ -1298,12 +1298,16 @@ class OpenChain:
 
 # ---------------------------------------------------------------------------------------- a float32 residual stream
 
-def embedding32(tokens, table, scale=1.0, status=None, fence=False):
+def embedding32(tokens, table, scale=1.0, status=None, fence=False, out=None):
     """``out[t] = float(table[tokens[t]]) * scale``: float32 ``[T, H]``, the start of a residual stream
-    that is kept in 32-bit whatever the working type.  ``fence`` as in ``embedding``."""
+    that is kept in 32-bit whatever the working type.  ``fence`` as in ``embedding``.  ``out``: where to
+    write (float32 ``[T, H]``, contiguous) instead of a new tensor."""
     _need(tokens, "tokens", torch.int32, 1)
     _need(table, "table", None, 2)
-    out = torch.empty((tokens.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
+    if out is None:
+        out = torch.empty((tokens.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
+    else:
+        _f32(out, "out", (tokens.shape[0], table.shape[1]))
     rc = _lib("residual32").sb_embed32(
         _code(table.dtype), _ptr(tokens), _ptr(table), _ptr(out), tokens.shape[0], table.shape[1],
         table.shape[0], ctypes.c_float(scale), _ptr(status), int(fence), _stream())
@@ -1445,19 +1449,24 @@ def latent_max_row() -> int:
     return _lib("attention_latent").sb_latent_max_row()
 
 
+#: the pairings the latent-attention kernels turn, and the code they take for each
+LATENT_LAYOUTS = {"interleaved": 0, "half_split": 1}
+
+
 def latent_tables(rotation, rot_dims: int):
     """``(cos, sin)`` for the latent-attention kernels: they turn the first ``rot_dims`` entries of the
-    rotated part in interleaved layout (entry ``2i`` with ``2i + 1``)."""
+    rotated part, entry ``2i`` with ``2i + 1`` (``"interleaved"``) or ``i`` with ``i + rot_dims / 2``
+    (``"half_split"``); ``latent_prepare`` and ``latent_rotate_q`` take the layout's name."""
     if rotation is None:
         raise KernelError("latent attention needs a position part that offers a rotation")
-    if rotation.layout != "interleaved" or rotation.rotary_dim != rot_dims:
-        raise KernelError(f"the latent-attention kernels turn {rot_dims} entries in interleaved layout; asked for "
-                          f"{rotation.rotary_dim} in {rotation.layout!r} layout")
+    if rotation.layout not in LATENT_LAYOUTS or rotation.rotary_dim != rot_dims:
+        raise KernelError(f"the latent-attention kernels turn {rot_dims} entries in interleaved or half-split layout; "
+                          f"asked for {rotation.rotary_dim} in {rotation.layout!r} layout")
     return rotation.cos, rotation.sin
 
 
 def latent_prepare(proj, q_gain, kv_gain, eps, cos_table, sin_table, tok_pos, tok_slot, block_table, store,
-                   q_rank, rank, rot, rot_dims, write_cache=True):
+                   q_rank, rank, rot, rot_dims, write_cache=True, layout="interleaved"):
     """What follows a token's stacked down-projections ``proj`` = ``[query latent | key/value latent | shared
     key part]`` (the query latent alone with ``write_cache`` false): returns the RMS-normed query latent
     ``[T, q_rank]``; norms the key/value latent, turns the shared key part by the token's position and files
@@ -1485,12 +1494,12 @@ def latent_prepare(proj, q_gain, kv_gain, eps, cos_table, sin_table, tok_pos, to
         _code(proj.dtype), _ptr(proj), proj.shape[1], _ptr(q_gain), _ptr(kv_gain if write_cache else None),
         ctypes.c_float(eps), _ptr(cos_table), _ptr(sin_table), cos_table.shape[1], _ptr(tok_pos), _ptr(tok_slot),
         _ptr(block_table), block_table.shape[1], _ptr(store if write_cache else None), _ptr(cq), n_tokens, q_rank,
-        rank, rot, rot_dims, int(write_cache), _stream())
+        rank, rot, rot_dims, int(write_cache), LATENT_LAYOUTS[layout], _stream())
     _check(rc, "latent_prepare")
     return cq
 
 
-def latent_rotate_q(q, qa, cos_table, sin_table, tok_pos, heads, dim, rot, rot_dims, rank):
+def latent_rotate_q(q, qa, cos_table, sin_table, tok_pos, heads, dim, rot, rot_dims, rank, layout="interleaved"):
     """Turns the last ``rot`` entries of every head of ``q`` ``[T, heads * (dim + rot)]`` by the token's
     position and files them behind the first ``rank`` entries of that head in ``qa`` ``[T, heads, rank + rot]``."""
     _need(q, "q", None, 2)
@@ -1499,7 +1508,7 @@ def latent_rotate_q(q, qa, cos_table, sin_table, tok_pos, heads, dim, rot, rot_d
         raise KernelError(f"q {tuple(q.shape)} / qa {tuple(qa.shape)} do not fit {heads} heads of {dim} + {rot}")
     rc = _lib("attention_latent").sb_latent_rotate_q(
         _code(q.dtype), _ptr(q), _ptr(qa), _ptr(cos_table), _ptr(sin_table), cos_table.shape[1], _ptr(tok_pos),
-        q.shape[0], heads, dim, rot, rot_dims, rank, _stream())
+        q.shape[0], heads, dim, rot, rot_dims, rank, LATENT_LAYOUTS[layout], _stream())
     _check(rc, "latent_rotate_q")
 
 
@@ -1595,9 +1604,18 @@ def moe_limits():
     return lib.sb_moe_max_experts(), lib.sb_moe_max_top()
 
 
-def moe_route(h, router, router_bias, top):
+#: how the chosen experts' weights are formed from their logits, and the code the router takes
+MOE_SCORINGS = {"softmax_top": 0, "sigmoid_normalised": 1}
+#: the experts the tile kernels know, and the code of their up pass
+MOE_EXPERTS = {"gated_clamped": 1, "relu2": 2}
+
+
+def moe_route(h, router, router_bias, top, scoring="softmax_top", weight_scale=1.0):
     """``(ids int32 [T, top], weights float32 [T, top])``: the ``top`` largest of ``router @ h + bias``
-    (float32 ``[E, W]`` and ``[E]``), and the softmax over those alone."""
+    (float32 ``[E, W]`` and ``[E]`` or None), and either the softmax over those alone or, with ``scoring``
+    ``"sigmoid_normalised"``, their sigmoids divided by their sum (+ 1e-20) times ``weight_scale``."""
+    if scoring not in MOE_SCORINGS:
+        raise KernelError(f"no router scoring {scoring!r} (known: {', '.join(MOE_SCORINGS)})")
     _need(h, "h", None, 2)
     experts = router.shape[0]
     _f32(router, "router", (experts, h.shape[1]))
@@ -1606,7 +1624,8 @@ def moe_route(h, router, router_bias, top):
     ids = torch.empty((h.shape[0], top), dtype=torch.int32, device=h.device)
     weights = torch.empty((h.shape[0], top), dtype=torch.float32, device=h.device)
     rc = _lib("moe").sb_moe_route(_code(h.dtype), _ptr(h), _ptr(router), _ptr(router_bias), _ptr(ids), _ptr(weights),
-                                  h.shape[0], h.shape[1], experts, top, _stream())
+                                  h.shape[0], h.shape[1], experts, top, MOE_SCORINGS[scoring],
+                                  ctypes.c_float(weight_scale), _stream())
     if rc == -2:
         raise KernelError(f"the router takes up to {moe_limits()[0]} experts and {moe_limits()[1]} choices, not "
                           f"{experts} and {top}")
@@ -1614,10 +1633,15 @@ def moe_route(h, router, router_bias, top):
     return ids, weights
 
 
-def moe_experts(h, ids, weights, gate_up, down, limit):
+def moe_experts(h, ids, weights, gate_up, down, limit=0.0, expert="gated_clamped"):
     """The chosen experts of every row and their weighted sum: ``gate_up`` ``[E, 2 * F, W]`` (an expert's
     gate rows, then its up rows), ``down`` ``[E, W, F]``; an expert is ``down(g * sigmoid(1.702 g) * (u +
-    1))`` with ``g = min(gate(h), limit)`` and ``u = clamp(up(h), -limit, limit)``.  Returns ``[T, W]``."""
+    1))`` with ``g = min(gate(h), limit)`` and ``u = clamp(up(h), -limit, limit)``.  With ``expert``
+    ``"relu2"`` the experts have no gate: ``gate_up`` is ``[E, F, W]`` and an expert is
+    ``down(relu(up(h))^2)``.  Returns ``[T, W]``."""
+    if expert not in MOE_EXPERTS:
+        raise KernelError(f"no expert kind {expert!r} (known: {', '.join(MOE_EXPERTS)})")
+    up_mode = MOE_EXPERTS[expert]
     _need(h, "h", None, 2)
     _need(gate_up, "gate_up", h.dtype, 3)
     _need(down, "down", h.dtype, 3)
@@ -1625,9 +1649,9 @@ def moe_experts(h, ids, weights, gate_up, down, limit):
     _need(weights, "weights", torch.float32, 2)
     n_tokens, width = h.shape
     experts, two_f, _ = gate_up.shape
-    inner = two_f // 2
+    inner = two_f // 2 if up_mode == 1 else two_f
     top = ids.shape[1]
-    if tuple(gate_up.shape) != (experts, 2 * inner, width) or tuple(down.shape) != (experts, width, inner):
+    if tuple(gate_up.shape) != (experts, (2 if up_mode == 1 else 1) * inner, width) or tuple(down.shape) != (experts, width, inner):
         raise KernelError(f"expert weights {tuple(gate_up.shape)} / {tuple(down.shape)} do not fit rows of {width}")
     lib = _lib("moe")
     bm = lib.sb_moe_tile_rows(_code(h.dtype), width, inner)     # 64: tensor-core tiles; 32: the plain ones
@@ -1640,7 +1664,7 @@ def moe_experts(h, ids, weights, gate_up, down, limit):
                           bm, _stream())
     _check(rc, "moe_align")
     act = torch.empty((capacity, inner), dtype=h.dtype, device=h.device)
-    rc = lib.sb_moe_tiles(_code(h.dtype), 1, bm, _ptr(h), _ptr(gate_up), _ptr(act), _ptr(sorted_pairs), _ptr(tile_expert),
+    rc = lib.sb_moe_tiles(_code(h.dtype), up_mode, bm, _ptr(h), _ptr(gate_up), _ptr(act), _ptr(sorted_pairs), _ptr(tile_expert),
                           _ptr(n_tiles), max_tiles, width, inner, top, ctypes.c_float(limit), _stream())
     _check(rc, "moe_up")
     per_pair = torch.empty((n_pairs, width), dtype=h.dtype, device=h.device)
@@ -1651,3 +1675,168 @@ def moe_experts(h, ids, weights, gate_up, down, limit):
     rc = lib.sb_moe_combine(_code(h.dtype), _ptr(per_pair), _ptr(weights), _ptr(out), n_tokens, width, top, _stream())
     _check(rc, "moe_combine")
     return out
+
+
+# ---------------------------------------------------------------------------------------- a stream joined over depth
+
+#: the norms ``depth_step`` can apply, and the code the kernel takes
+DEPTH_NORMS = {"rmsnorm": 0, "layernorm": 1}
+
+
+def depth_step(base, dtype, pending=None, mult=1.0, history=None, mix=None, dst=None, norm=None, rows=None):
+    """One kernel between two sublayers of a model whose float32 residual stream is joined over depth.
+
+    ``base`` float32 ``[T, H]``: the rows the sum starts from.  ``pending`` (``[T, H]`` in ``dtype``, or
+    None): the output of the sublayer before; ``v = base + mult * pending``.  With ``mix`` (float32
+    ``[levels]``) and ``history`` (float32 ``[>= levels, T, H]``): ``v`` is filed as ``history[levels - 1]``
+    and the stream becomes ``x = sum_j mix[j] * history[j]``; otherwise ``x = v``.  ``dst`` (float32 ``[T,
+    H]``, not ``base``): where ``x`` is written.  ``norm = (kind, gain, eps)`` with ``kind`` of
+    ``DEPTH_NORMS`` and a float32 gain: the norm of ``x`` is returned in ``dtype``.  With ``rows`` (int32
+    ``[R]``) only those rows are computed, nothing but the result is written, and it is ``[R, H]``."""
+    _need(base, "base", torch.float32, 2)
+    n_tokens, hidden = base.shape
+    if pending is not None:
+        _need(pending, "pending", dtype, 2)
+        if tuple(pending.shape) != (n_tokens, hidden):
+            raise KernelError(f"pending {tuple(pending.shape)} does not match the stream {tuple(base.shape)}")
+    levels = 0
+    if mix is not None:
+        _need(mix, "mix", torch.float32, 1)
+        levels = mix.shape[0]
+        _need(history, "history", torch.float32, 3)
+        if history.shape[0] < levels or tuple(history.shape[1:]) != (n_tokens, hidden):
+            raise KernelError(f"history {tuple(history.shape)} does not hold {levels} levels of {tuple(base.shape)}")
+    if dst is not None:
+        _f32(dst, "dst", (n_tokens, hidden))
+        if dst.data_ptr() == base.data_ptr():
+            raise KernelError("dst must not be base")
+    n_rows = n_tokens
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+        n_rows = rows.shape[0]
+    out = gain = None
+    eps, kind = 0.0, 0
+    if norm is not None:
+        name, gain, eps = norm
+        if name not in DEPTH_NORMS:
+            raise KernelError(f"no norm {name!r} here (known: {', '.join(DEPTH_NORMS)})")
+        kind = DEPTH_NORMS[name]
+        _f32(gain, "gain", (hidden,))
+        out = torch.empty((n_rows, hidden), dtype=dtype, device=base.device)
+    rc = _lib("depth").sb_depth_step(
+        _code(dtype), _ptr(base), _ptr(pending), ctypes.c_float(mult), _ptr(history if mix is not None else None),
+        ctypes.c_longlong(n_tokens * hidden), _ptr(mix), levels, _ptr(dst), _ptr(gain), _ptr(out), _ptr(rows), n_rows,
+        hidden, ctypes.c_float(eps), kind, _stream())
+    _check(rc, "depth_step")
+    return out
+
+
+def softcap(logits, cap):
+    """``logits <- cap * tanh(logits / cap)`` in place (float32)."""
+    _need(logits, "logits", torch.float32)
+    rc = _lib("depth").sb_softcap(_ptr(logits), ctypes.c_longlong(logits.numel()), ctypes.c_float(cap), _stream())
+    _check(rc, "softcap")
+    return logits
+
+
+def gated_clamped(gate_up, limit):
+    """``g * sigmoid(1.702 g) * (u + 1)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)`` for
+    ``gate_up = [gate | up]`` of shape ``[T, 2 * I]``."""
+    _need(gate_up, "gate_up", None, 2)
+    if gate_up.shape[1] % 2:
+        raise KernelError(f"gate_up has an odd width {gate_up.shape[1]}")
+    inner = gate_up.shape[1] // 2
+    out = torch.empty((gate_up.shape[0], inner), dtype=gate_up.dtype, device=gate_up.device)
+    rc = _lib("elementwise").sb_gated_clamped(_code(gate_up.dtype), _ptr(gate_up), _ptr(out), gate_up.shape[0], inner,
+                                              ctypes.c_float(limit), _stream())
+    _check(rc, "gated_clamped")
+    return out
+
+
+# ---------------------------------------------------------------------------------------- attention with a sink
+
+def sink_max_dim() -> int:
+    return _lib("attention_sink").sb_sink_max_dim()
+
+
+def sink_prepare(proj, heads, kv_heads, dim, vdim, tok_pos, tok_slot, block_table, k_store, v_store, gated=True,
+                 write_cache=True):
+    """What follows a token's stacked projections ``proj`` = ``[q | k | v | g]`` (``[q | g]`` with
+    ``write_cache`` false; no ``g`` with ``gated`` false): files the keys and values in the token's cache
+    row (``k_store`` ``[pages, kv_heads, 64, dim]``, ``v_store`` ``[pages, kv_heads, 64, vdim]``) and returns
+    the gates ``sigmoid(g)`` as float32 ``[T, heads]`` (None without).  The queries stay where they are."""
+    _need(proj, "proj", None, 2)
+    n_tokens = proj.shape[0]
+    want = heads * dim + (kv_heads * (dim + vdim) if write_cache else 0) + (heads if gated else 0)
+    if proj.shape[1] != want:
+        raise KernelError(f"proj has width {proj.shape[1]}, expected {want}")
+    _need(tok_pos, "tok_pos", torch.int32, 1)
+    _need(tok_slot, "tok_slot", torch.int32, 1)
+    _need(block_table, "block_table", torch.int32, 2)
+    if write_cache:
+        _need(k_store, "key pages", proj.dtype, 4)
+        _need(v_store, "value pages", proj.dtype, 4)
+        if tuple(k_store.shape[1:]) != (kv_heads, PAGE_TOKENS, dim) or tuple(v_store.shape[1:]) != (kv_heads, PAGE_TOKENS, vdim):
+            raise KernelError(f"cache pages have shapes {tuple(k_store.shape)} / {tuple(v_store.shape)}, expected "
+                              f"[pages, {kv_heads}, {PAGE_TOKENS}, {dim}] / [.., {vdim}]")
+    gate = torch.empty((n_tokens, heads), dtype=torch.float32, device=proj.device) if gated else None
+    rc = _lib("attention_sink").sb_sink_prepare(
+        _code(proj.dtype), _ptr(proj), proj.shape[1], _ptr(tok_pos), _ptr(tok_slot), _ptr(block_table),
+        block_table.shape[1], _ptr(k_store if write_cache else None), _ptr(v_store if write_cache else None),
+        _ptr(gate), n_tokens, heads, kv_heads, dim, vdim, int(write_cache), _stream())
+    _check(rc, "sink_prepare")
+    return gate
+
+
+def _sink_check(q, k_store, v_store, heads, kv_heads, dim, vdim, penalty, sink, gate):
+    _need(q, "q", None, 2)
+    if q.shape[1] < heads * dim:
+        raise KernelError(f"q rows of {q.shape[1]} entries do not hold {heads} heads of {dim}")
+    _need(k_store, "key pages", q.dtype, 4)
+    _need(v_store, "value pages", q.dtype, 4)
+    if tuple(k_store.shape[1:]) != (kv_heads, PAGE_TOKENS, dim) or tuple(v_store.shape[1:]) != (kv_heads, PAGE_TOKENS, vdim):
+        raise KernelError(f"cache pages have shapes {tuple(k_store.shape)} / {tuple(v_store.shape)}")
+    r1 = r2 = None
+    if penalty is not None:
+        r1, r2 = penalty
+        _f32(r1, "r1", (heads,))
+        _f32(r2, "r2", (heads,))
+    if sink is not None:
+        _f32(sink, "sink", (heads,))
+    if gate is not None:
+        _f32(gate, "gate", (q.shape[0], heads))
+    return r1, r2
+
+
+def sink_attention(q, k_store, v_store, block_table, tok_slot, tok_pos, heads, kv_heads, dim, vdim, scale,
+                   penalty=None, sink=None, gate=None, chunk=None, window=None):
+    """Attention of every query row over its sequence's cached keys, plain kernel (any sizes up to
+    ``sink_max_dim()``, both types).  ``q``: rows whose first ``heads * dim`` entries are the queries (a
+    stacked projection may carry more behind them).  ``penalty = (r1, r2)``: ``r1_h ln(1 + r2_h (i - j))`` is
+    taken off the scaled scores; ``sink``: one more term ``exp(sink_h)`` in the softmax's denominator;
+    ``gate`` float32 ``[T, heads]``: multiplies the head's output; ``chunk``: keys of the query's own chunk of
+    that many positions only; ``window``: the most recent that many keys.  Returns ``[T, heads * vdim]``."""
+    r1, r2 = _sink_check(q, k_store, v_store, heads, kv_heads, dim, vdim, penalty, sink, gate)
+    _need(block_table, "block_table", torch.int32, 2)
+    _need(tok_slot, "tok_slot", torch.int32, 1)
+    _need(tok_pos, "tok_pos", torch.int32, 1)
+    out = torch.empty((q.shape[0], heads * vdim), dtype=q.dtype, device=q.device)
+    rc = _lib("attention_sink").sb_sink_attention(
+        _code(q.dtype), _ptr(q), q.shape[1], _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
+        block_table.shape[1], _ptr(tok_slot), _ptr(tok_pos), _ptr(r1), _ptr(r2), _ptr(sink), _ptr(gate), q.shape[0],
+        heads, kv_heads, dim, vdim, ctypes.c_float(scale), int(chunk or 0), int(window or 0), _stream())
+    _check(rc, "sink_attention")
+    return out
+
+
+def sink_attention_step(q, k_store, v_store, block_table, ctx, heads, kv_heads, dim, vdim, scale, penalty=None,
+                        sink=None, gate=None, chunk=None, window=None):
+    """``sink_attention`` for the step ``ctx`` describes, on the kernel that fits its shape."""
+    return sink_attention(q, k_store, v_store, block_table, ctx.tok_slot, ctx.tok_pos, heads, kv_heads, dim, vdim,
+                          scale, penalty, sink, gate, chunk, window)
+
+
+def linear_gated_clamped(x, weight, limit, status=None):
+    """``g * sigmoid(1.702 g) * (u + 1)`` with ``g = min(x @ gate.T, limit)`` and ``u = clamp(x @ up.T, -limit,
+    limit)`` for ``weight = [gate; up]`` stacked (``[2 * I, K]``); returns ``[T, I]``."""
+    return gated_clamped(linear(x, weight, status=status), limit)

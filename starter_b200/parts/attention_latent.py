@@ -80,17 +80,18 @@ class LatentAttention(Part):
         store, _ = cache.entry_pages(entry)
         weight = self.down if writes_cache else self.down[: s.q_rank]
         proj = ops.linear(x, weight, status=ctx.status)
-        cos, sin = ops.latent_tables(self.position.rotation(), s.position.dims)
+        rotation = self.position.rotation()
+        cos, sin = ops.latent_tables(rotation, s.position.dims)
         cq = ops.latent_prepare(proj, self.q_gain, self.kv_gain, s.norm_eps, cos, sin, ctx.tok_pos, ctx.tok_slot,
                                 cache.block_table, store, s.q_rank, s.kv_rank, s.rot_dim, s.position.dims,
-                                write_cache=writes_cache)
+                                write_cache=writes_cache, layout=rotation.layout)
         q = ops.linear(cq, self.uq, status=ctx.status)
         n = q.shape[0]
         qa = torch.empty((n, s.num_heads, self.row), dtype=q.dtype, device=q.device)
         q3 = q.view(n, s.num_heads, s.head_dim + s.rot_dim)
         torch.bmm(q3[:, :, : s.head_dim].transpose(0, 1), self.uk, out=qa[:, :, : s.kv_rank].transpose(0, 1))
         ops.latent_rotate_q(q, qa, cos, sin, ctx.tok_pos, s.num_heads, s.head_dim, s.rot_dim, s.position.dims,
-                            s.kv_rank)
+                            s.kv_rank, layout=rotation.layout)
         summed = ops.latent_attention_step(qa, store, cache.block_table, ctx, s.num_heads, s.kv_rank, s.rot_dim,
                                            s.scale, s.window)
         a = torch.empty((n, s.num_heads, s.value_dim), dtype=q.dtype, device=q.device)

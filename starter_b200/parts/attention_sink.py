@@ -1,0 +1,90 @@
+"""Grouped-query attention without rotation whose positions enter through the scores and the mask: a
+logarithmic distance penalty per head, chunks of the sequence, a sink in the softmax, a sigmoid gate per
+head (each optional, see ``SinkAttentionSpec``).
+
+One step of it: one stacked product gives ``[q | k | v | g]``; ``ops.sink_prepare`` files keys and values
+at each token's own position and forms the gates; the attention kernel reads the queries from the stacked
+rows, the keys and values from the cache, and applies the gate; the output projection follows.  A whole
+prompt, a later portion and a single token are the same code: every query is told its absolute position,
+and chunks are counted from the sequence's start.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..cache.layout import KVNeed
+from .base import ParamSpec, Part, bytes_of
+
+
+class SinkAttention(Part):
+    def __init__(self, spec, dtype, position=None):
+        super().__init__(spec, dtype)
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError(f"{spec.num_heads} query heads cannot share {spec.num_kv_heads} key/value heads")
+        if position is not None or spec.position is not None:
+            raise ValueError("this attention takes no rotation: positions enter through its scores and mask")
+        if max(spec.head_dim, spec.value_dim) > 256:
+            raise ValueError(f"head sizes {spec.head_dim} / {spec.value_dim} exceed the 256 entries the kernels take")
+        self.q_size = spec.num_heads * spec.head_dim
+        self.kv_size = spec.num_kv_heads * (spec.head_dim + spec.value_dim)
+        self.penalty = self.sink = None
+
+    def kv_need(self):
+        s = self.spec
+        # every key stays: a later query of the same chunk may still read it (chunks bound what is read)
+        return KVNeed(s.num_kv_heads, s.head_dim, s.window, s.value_dim)
+
+    def state_need(self):
+        return None
+
+    def param_specs(self):
+        s = self.spec
+        out = {
+            "q": ParamSpec((self.q_size, s.hidden_size)),
+            "k": ParamSpec((s.num_kv_heads * s.head_dim, s.hidden_size)),
+            "v": ParamSpec((s.num_kv_heads * s.value_dim, s.hidden_size)),
+            "o": ParamSpec((s.hidden_size, s.num_heads * s.value_dim)),
+        }
+        if s.distance_penalty:
+            out["r1"] = ParamSpec((s.num_heads,), "vector32")
+            out["r2"] = ParamSpec((s.num_heads,), "slope")
+        if s.sink:
+            out["sink"] = ParamSpec((s.num_heads,), "vector32")
+        if s.head_gate:
+            out["g"] = ParamSpec((s.num_heads, s.hidden_size))
+        return out
+
+    def set_params(self, params):
+        s = self.spec
+        rows = [params["q"], params["k"], params["v"]] + ([params["g"]] if s.head_gate else [])
+        self.qkvg = torch.cat(rows, dim=0).contiguous()
+        # the rows a layer that only reads another layer's cache needs: queries and gates
+        self.qg = torch.cat([params["q"], params["g"]], dim=0).contiguous() if s.head_gate else None
+        self.o = params["o"].contiguous()
+        if s.distance_penalty:
+            self.penalty = (params["r1"].float().contiguous(), params["r2"].float().contiguous())
+        if s.sink:
+            self.sink = params["sink"].float().contiguous()
+
+    def prepare(self, max_position: int) -> bool:
+        return False
+
+    def __call__(self, x, ctx, entry, writes_cache=True):
+        s = self.spec
+        cache = ctx.cache
+        keys, values = cache.entry_pages(entry)
+        if writes_cache:
+            weight = self.qkvg
+        else:
+            weight = self.qg if s.head_gate else self.qkvg[: self.q_size]
+        proj = ops.linear(x, weight, status=ctx.status)
+        gate = ops.sink_prepare(proj, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, ctx.tok_pos, ctx.tok_slot,
+                                cache.block_table, keys, values, gated=s.head_gate, write_cache=writes_cache)
+        a = ops.sink_attention_step(proj, keys, values, cache.block_table, ctx, s.num_heads, s.num_kv_heads,
+                                    s.head_dim, s.value_dim, s.scale, self.penalty, self.sink, gate, s.chunk, s.window)
+        return ops.linear(a, self.o, status=ctx.status)
+
+    def weight_bytes(self):
+        return bytes_of(self.qkvg, self.o, self.sink, *(self.penalty or ()))

@@ -38,6 +38,27 @@ class GatedFeedForward(Part):
         return bytes_of(self.gate_up, self.down)
 
 
+class ClampedGatedFeedForward(Part):
+    """``down(g * sigmoid(1.702 g) * (u + 1))`` with ``g = min(gate(x), limit)``, ``u = clamp(up(x), -limit,
+    limit)``; gate and up are stored stacked so that one product feeds both."""
+
+    def param_specs(self):
+        h, i = self.spec.hidden_size, self.spec.intermediate_size
+        return {"gate": ParamSpec((i, h)), "up": ParamSpec((i, h)), "down": ParamSpec((h, i))}
+
+    def set_params(self, params):
+        self.gate_up = torch.cat([params["gate"], params["up"]], dim=0).contiguous()
+        self.down = params["down"].contiguous()
+
+    def __call__(self, x, ctx=None):
+        status = ctx.status if ctx is not None else None
+        act = ops.linear_gated_clamped(x, self.gate_up, self.spec.limit, status=status)
+        return ops.linear(act, self.down, status=status)
+
+    def weight_bytes(self):
+        return bytes_of(self.gate_up, self.down)
+
+
 class BiasedFeedForward(Part):
     """``down(act(up(x) + b_up)) + b_down`` with the activation of the spec (``relu2``: the square of relu).
     The down bias can be left to whoever writes the output to the residual stream (``defer_bias``)."""
@@ -71,24 +92,30 @@ class BiasedFeedForward(Part):
 
 
 class RoutedExperts(Part):
-    """A mixture of small gated experts: the router's logits in 32-bit, the ``top`` largest, softmax over
-    those; the chosen experts of all tokens run as tiles grouped by expert (``ops.moe_experts``), without a
-    word from the host, so the part also runs inside a captured step."""
+    """A mixture of small experts: the router's logits in 32-bit, the ``top`` largest, their weights by the
+    spec's ``scoring``; the chosen experts of all tokens run as tiles grouped by expert (``ops.moe_experts``),
+    without a word from the host, so the part also runs inside a captured step.  The experts are gated and
+    clamped, or (``expert = "relu2"``) an up and a down projection around a squared relu."""
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
         if spec.top > spec.experts:
             raise ValueError(f"{spec.top} choices among {spec.experts} experts")
+        if spec.expert not in ops.MOE_EXPERTS or spec.scoring not in ops.MOE_SCORINGS:
+            raise ValueError(f"no routed experts of kind {spec.expert!r} with scoring {spec.scoring!r}")
+        self.gated = spec.expert == "gated_clamped"
         #: the experts chosen in the latest call (int32 ``[T, top]``, on the device), for whoever wants to
         #: look at the routing
         self.last_ids = None
 
     def param_specs(self):
         s = self.spec
-        out = {"router": ParamSpec((s.experts, s.hidden_size), "matrix32"),
-               "router_bias": ParamSpec((s.experts,), "bias32")}
+        out = {"router": ParamSpec((s.experts, s.hidden_size), "matrix32")}
+        if s.router_bias:
+            out["router_bias"] = ParamSpec((s.experts,), "bias32")
         for e in range(s.experts):
-            out[f"e{e}_gate"] = ParamSpec((s.intermediate_size, s.hidden_size))
+            if self.gated:
+                out[f"e{e}_gate"] = ParamSpec((s.intermediate_size, s.hidden_size))
             out[f"e{e}_up"] = ParamSpec((s.intermediate_size, s.hidden_size))
             out[f"e{e}_down"] = ParamSpec((s.hidden_size, s.intermediate_size))
         return out
@@ -96,16 +123,19 @@ class RoutedExperts(Part):
     def set_params(self, params):
         s = self.spec
         self.router = params["router"].float().contiguous()
-        self.router_bias = params["router_bias"].float().contiguous()
-        self.gate_up = torch.stack([torch.cat([params[f"e{e}_gate"], params[f"e{e}_up"]], dim=0)
-                                    for e in range(s.experts)]).contiguous()
+        self.router_bias = params["router_bias"].float().contiguous() if s.router_bias else None
+        if self.gated:
+            self.gate_up = torch.stack([torch.cat([params[f"e{e}_gate"], params[f"e{e}_up"]], dim=0)
+                                        for e in range(s.experts)]).contiguous()
+        else:
+            self.gate_up = torch.stack([params[f"e{e}_up"] for e in range(s.experts)]).contiguous()
         self.down = torch.stack([params[f"e{e}_down"] for e in range(s.experts)]).contiguous()
 
     def __call__(self, x, ctx=None):
         s = self.spec
-        ids, weights = ops.moe_route(x, self.router, self.router_bias, s.top)
+        ids, weights = ops.moe_route(x, self.router, self.router_bias, s.top, s.scoring, s.weight_scale)
         self.last_ids = ids
-        return ops.moe_experts(x, ids, weights, self.gate_up, self.down, s.limit)
+        return ops.moe_experts(x, ids, weights, self.gate_up, self.down, s.limit, s.expert)
 
     def weight_bytes(self):
         """What a step reads at most: the router and every expert (a step of few tokens reads only the

@@ -26,12 +26,15 @@ from __future__ import annotations
 from .attention import GroupedQueryAttention
 from .attention_diff import DifferentialAttention
 from .attention_latent import LatentAttention
+from .attention_sink import SinkAttention
 from .block import PreNormBlock
-from .feedforward import BiasedFeedForward, GatedFeedForward, RoutedExperts
+from .depth import DepthAverage, DepthMixerOnlyBlock, DepthPreNormBlock
+from .feedforward import BiasedFeedForward, ClampedGatedFeedForward, GatedFeedForward, RoutedExperts
 from .hyper import HyperConnection, HyperMixerOnlyBlock, HyperPreNormBlock
 from .norm import RMSNorm
 from .norm_dyt import DynamicTanh
-from .rotary import InterleavedRotaryTable, RotaryTable
+from .norm_layer import LayerNorm
+from .rotary import InterleavedRotaryTable, PartialRotaryTable, RotaryTable
 from .sandwich import SandwichBlock, SandwichMixerOnlyBlock
 from .wkv import WkvMixer
 
@@ -70,3 +73,10 @@ register("feed_forward", "routed_experts", RoutedExperts)
 register("position", "rope_interleaved", InterleavedRotaryTable)
 register("arrangement", "sandwich", SandwichBlock)
 register("arrangement", "sandwich_mixer_only", SandwichMixerOnlyBlock)
+register("mixer", "sink_attention", SinkAttention)
+register("feed_forward", "gated_clamped", ClampedGatedFeedForward)
+register("norm", "layernorm", LayerNorm)
+register("position", "rope_partial", PartialRotaryTable)
+register("connection", "depth_average", DepthAverage)
+register("arrangement", "depth_prenorm", DepthPreNormBlock)
+register("arrangement", "depth_mixer_only", DepthMixerOnlyBlock)

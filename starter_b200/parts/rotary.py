@@ -89,3 +89,11 @@ class InterleavedRotaryTable(RotaryTable):
         self.sin = angles.sin().float().contiguous().to(self.device)
         self.length = size
         return True
+
+
+class PartialRotaryTable(InterleavedRotaryTable):
+    """Tables for a rotation of entry ``i`` with entry ``i + dims / 2`` over the first ``dims`` entries of a
+    vector: the same angles ``position * base ** (-2i / dims)`` as the interleaved tables, paired half-split."""
+
+    def rotation(self) -> Rotation:
+        return Rotation(self.cos, self.sin, self.spec.dims, "half_split")
