@@ -55,6 +55,7 @@ SOURCES = (
     "moe",
     "depth",
     "attention_sink",
+    "attention_sink_tc",
 )
 
 _lock = threading.Lock()

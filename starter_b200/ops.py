@@ -1762,14 +1762,14 @@ def sink_max_dim() -> int:
 def sink_prepare(proj, heads, kv_heads, dim, vdim, tok_pos, tok_slot, block_table, k_store, v_store, gated=True,
                  write_cache=True):
     """What follows a token's stacked projections ``proj`` = ``[q | k | v | g]`` (``[q | g]`` with
-    ``write_cache`` false; no ``g`` with ``gated`` false): files the keys and values in the token's cache
+    ``write_cache`` false; no ``g`` with ``gated`` false; up to 7 unused entries may follow): files the keys and values in the token's cache
     row (``k_store`` ``[pages, kv_heads, 64, dim]``, ``v_store`` ``[pages, kv_heads, 64, vdim]``) and returns
     the gates ``sigmoid(g)`` as float32 ``[T, heads]`` (None without).  The queries stay where they are."""
     _need(proj, "proj", None, 2)
     n_tokens = proj.shape[0]
     want = heads * dim + (kv_heads * (dim + vdim) if write_cache else 0) + (heads if gated else 0)
-    if proj.shape[1] != want:
-        raise KernelError(f"proj has width {proj.shape[1]}, expected {want}")
+    if not want <= proj.shape[1] < want + 8:
+        raise KernelError(f"proj has width {proj.shape[1]}, expected {want} (and up to 7 entries of padding)")
     _need(tok_pos, "tok_pos", torch.int32, 1)
     _need(tok_slot, "tok_slot", torch.int32, 1)
     _need(block_table, "block_table", torch.int32, 2)
@@ -1829,9 +1829,68 @@ def sink_attention(q, k_store, v_store, block_table, tok_slot, tok_pos, heads, k
     return out
 
 
+SINK_TC_DIMS = (16, 32, 64, 128)
+
+
+def sink_tc_takes(q, heads, kv_heads, dim, vdim) -> bool:
+    """Whether the tensor-core kernel takes these operands: bfloat16, ``dim`` and ``vdim`` of 16, 32, 64 or
+    128, up to 64 query heads a key/value head, query rows that start on 16-byte boundaries."""
+    return (q.dtype == torch.bfloat16 and dim in SINK_TC_DIMS and vdim in SINK_TC_DIMS and heads // kv_heads <= 64
+            and q.shape[1] % 8 == 0 and q.data_ptr() % 16 == 0)
+
+
+def sink_splits(rows: int, kv_heads: int, chunk, window, kv_hint: int) -> int:
+    """Into how many parts the pages of a single-token step are cut: enough blocks for two an SM, no part
+    shorter than a page, at most 16."""
+    keys = max(kv_hint, 1)
+    for bound in (chunk, window):
+        if bound:
+            keys = min(keys, bound)
+    pages = -(-keys // PAGE_TOKENS) + 1
+    return max(1, min(16, (2 * 148) // max(1, rows * kv_heads), pages))
+
+
+def sink_attention_tc(q, k_store, v_store, block_table, seq_slot, seq_q_start, seq_q_len, seq_kv_len, tile_seq,
+                      tile_first, heads, kv_heads, dim, vdim, scale, penalty=None, sink=None, gate=None, chunk=None,
+                      window=None, n_splits=1, max_q_len=0):
+    """``sink_attention`` on tensor cores (bfloat16): a block takes one key/value head and the query heads
+    that share it for consecutive tokens of a sequence (up to 64 rows), so a page is fetched once for all
+    of them.  The ``seq_*`` arrays describe the sequences of the step, ``tile_seq`` / ``tile_first`` list
+    its tiles of 64 tokens.  ``n_splits`` > 1 deals the pages of every block out to that many blocks, which
+    a second kernel joins: for steps of few rows."""
+    r1, r2 = _sink_check(q, k_store, v_store, heads, kv_heads, dim, vdim, penalty, sink, gate)
+    if not sink_tc_takes(q, heads, kv_heads, dim, vdim):
+        raise KernelError(f"the tensor-core attention takes bfloat16 heads of 16, 32, 64 or 128 entries in rows "
+                          f"that are multiples of 8 wide; got {q.dtype}, {dim} / {vdim}, rows of {q.shape[1]}")
+    _need(block_table, "block_table", torch.int32, 2)
+    for name, t in (("seq_slot", seq_slot), ("seq_q_start", seq_q_start), ("seq_q_len", seq_q_len),
+                    ("seq_kv_len", seq_kv_len), ("tile_seq", tile_seq), ("tile_first", tile_first)):
+        _need(t, name, torch.int32, 1)
+    n_tokens = q.shape[0]
+    out = torch.empty((n_tokens, heads * vdim), dtype=q.dtype, device=q.device)
+    part_acc = part_ml = None
+    n_splits = max(1, int(n_splits))
+    if n_splits > 1:
+        part_acc = torch.empty((n_splits, n_tokens * heads, vdim), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n_splits, n_tokens * heads, 2), dtype=torch.float32, device=q.device)
+    rc = _lib("attention_sink_tc").sb_sink_attention_tc(
+        _ptr(q), q.shape[1], _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(k_store), _ptr(v_store), _ptr(block_table),
+        block_table.shape[1], _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(tile_seq),
+        _ptr(tile_first), tile_seq.shape[0], _ptr(r1), _ptr(r2), _ptr(sink), _ptr(gate), n_tokens, heads, kv_heads,
+        dim, vdim, ctypes.c_float(scale), int(chunk or 0), int(window or 0), n_splits, int(max_q_len), _stream())
+    _check(rc, "sink_attention_tc", 2 if n_splits > 1 else 1)
+    return out
+
+
 def sink_attention_step(q, k_store, v_store, block_table, ctx, heads, kv_heads, dim, vdim, scale, penalty=None,
                         sink=None, gate=None, chunk=None, window=None):
-    """``sink_attention`` for the step ``ctx`` describes, on the kernel that fits its shape."""
+    """``sink_attention`` for the step ``ctx`` describes, on the kernel that fits its shape: tensor cores for
+    bfloat16 at sizes they take, the plain kernel otherwise (float32, other sizes)."""
+    if sink_tc_takes(q, heads, kv_heads, dim, vdim):
+        splits = sink_splits(ctx.n_seqs, kv_heads, chunk, window, ctx.max_kv_len) if ctx.max_q_len == 1 else 1
+        return sink_attention_tc(q, k_store, v_store, block_table, ctx.seq_slot, ctx.seq_q_start, ctx.seq_q_len,
+                                 ctx.seq_kv_len, ctx.tile_seq, ctx.tile_first, heads, kv_heads, dim, vdim, scale,
+                                 penalty, sink, gate, chunk, window, splits, ctx.max_q_len)
     return sink_attention(q, k_store, v_store, block_table, ctx.tok_slot, ctx.tok_pos, heads, kv_heads, dim, vdim,
                           scale, penalty, sink, gate, chunk, window)
 

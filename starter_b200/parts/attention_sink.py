@@ -58,10 +58,17 @@ class SinkAttention(Part):
 
     def set_params(self, params):
         s = self.spec
-        rows = [params["q"], params["k"], params["v"]] + ([params["g"]] if s.head_gate else [])
-        self.qkvg = torch.cat(rows, dim=0).contiguous()
+        def stacked(rows):
+            # rows of zeros bring the product's width to a multiple of 8, so that every token's queries
+            # start on a 16-byte boundary for the kernels that copy them in 16-byte pieces
+            pad = -sum(r.shape[0] for r in rows) % 8
+            if pad:
+                rows = rows + [torch.zeros((pad, s.hidden_size), dtype=rows[0].dtype, device=rows[0].device)]
+            return torch.cat(rows, dim=0).contiguous()
+
+        self.qkvg = stacked([params["q"], params["k"], params["v"]] + ([params["g"]] if s.head_gate else []))
         # the rows a layer that only reads another layer's cache needs: queries and gates
-        self.qg = torch.cat([params["q"], params["g"]], dim=0).contiguous() if s.head_gate else None
+        self.qg = stacked([params["q"]] + ([params["g"]] if s.head_gate else []))
         self.o = params["o"].contiguous()
         if s.distance_penalty:
             self.penalty = (params["r1"].float().contiguous(), params["r2"].float().contiguous())
@@ -75,10 +82,7 @@ class SinkAttention(Part):
         s = self.spec
         cache = ctx.cache
         keys, values = cache.entry_pages(entry)
-        if writes_cache:
-            weight = self.qkvg
-        else:
-            weight = self.qg if s.head_gate else self.qkvg[: self.q_size]
+        weight = self.qkvg if writes_cache else self.qg
         proj = ops.linear(x, weight, status=ctx.status)
         gate = ops.sink_prepare(proj, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, ctx.tok_pos, ctx.tok_slot,
                                 cache.block_table, keys, values, gated=s.head_gate, write_cache=writes_cache)

@@ -77,9 +77,38 @@ def sink_softmax(scores, visible, sink):
     return e / (e.sum(dim=-1, keepdim=True) + torch.exp(sink.reshape(-1, 1, 1) - top))
 
 
+def attend(q, k, v, scale, r1=None, r2=None, sink=None, gate=None, chunk=None, window=None, start=0):
+    """``q`` ``[Tq, H, D]`` are the queries of positions ``start .. start + Tq - 1``; ``k`` ``[T, G, D]`` and ``v``
+    ``[T, G, Dv]`` the keys and values of positions ``0 .. T - 1``.  ``score = q . k * scale - r1 ln(1 + r2 (i -
+    j))``; key ``j`` counts for query ``i`` when ``j <= i``, both lie in the same chunk and ``j > i - window``;
+    the softmax has one more term ``exp(sink)`` without a value; the head's output is multiplied by ``gate``
+    ``[Tq, H]``.  Returns ``[Tq, H, Dv]``."""
+    tq, heads, _ = q.shape
+    t, kv_heads, _ = k.shape
+    group = heads // kv_heads
+    out = torch.zeros(tq, heads, v.shape[2], dtype=F)
+    for a in range(tq):
+        i = start + a
+        for h in range(heads):
+            g = h // group
+            js = [j for j in range(min(i + 1, t)) if (chunk is None or j // chunk == i // chunk)
+                  and (window is None or j > i - window)]
+            s = torch.stack([(q[a, h] * k[j, g]).sum() * scale for j in js])
+            if r1 is not None:
+                d = torch.tensor([float(i - j) for j in js], dtype=F)
+                s = s - r1[h] * torch.log1p(r2[h] * d)
+            top = s.max() if sink is None else torch.maximum(s.max(), sink[h])
+            e = torch.exp(s - top)
+            denom = e.sum() + (torch.exp(sink[h] - top) if sink is not None else 0.0)
+            o = sum(e[n] * v[j, g] for n, j in enumerate(js)) / denom
+            out[a, h] = o * (gate[a, h] if gate is not None else 1.0)
+    return out
+
+
 def chunk_attention(h, w, prefix, m):
     """Grouped-query attention without rotation: ``score = q . k * scale - r1 ln(1 + r2 (i - j))``, keys of
-    the query's own chunk, a sink per head, the head's output times ``sigmoid(g . h)``."""
+    the query's own chunk, a sink per head, the head's output times ``sigmoid(g . h)``.  (The same as
+    ``attend``, in matrix form.)"""
     t = h.shape[0]
     heads, kv_heads, dim, vdim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = (h @ w[prefix + "q"].T).reshape(t, heads, dim)
