@@ -26,7 +26,8 @@ template <typename T>
 __global__ void sink_prepare_kernel(const T* __restrict__ proj, int proj_width, const int* __restrict__ tok_pos,
                                     const int* __restrict__ tok_slot, const int* __restrict__ block_table,
                                     int table_stride, T* __restrict__ k_store, T* __restrict__ v_store,
-                                    float* __restrict__ gate, int heads, int kv_heads, int dim, int vdim, int write) {
+                                    float* __restrict__ gate, int heads, int kv_heads, int dim, int vdim, int write,
+                                    int vec) {
   pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(proj);
   SB_BEHIND_WAIT(tok_pos);
@@ -42,13 +43,28 @@ __global__ void sink_prepare_kernel(const T* __restrict__ proj, int proj_width, 
     const int off = pos % SB_PAGE_TOKENS;
     const T* k = pr + q_width;
     const T* v = k + kv_heads * dim;
-    for (int e = threadIdx.x; e < kv_heads * dim; e += blockDim.x) {
-      const int h = e / dim, d = e - h * dim;
-      k_store[page_row(page, h, off, kv_heads, dim) + d] = k[e];
-    }
-    for (int e = threadIdx.x; e < kv_heads * vdim; e += blockDim.x) {
-      const int h = e / vdim, d = e - h * vdim;
-      v_store[page_row(page, h, off, kv_heads, vdim) + d] = v[e];
+    constexpr int N = 16 / sizeof(T);       // entries of a 16-byte piece
+    if (vec) {
+      // rows, head sizes and bases in whole 16-byte pieces: a piece a thread
+      for (int e = threadIdx.x; e < kv_heads * dim / N; e += blockDim.x) {
+        const int h = e / (dim / N), d = (e - h * (dim / N)) * N;
+        *reinterpret_cast<uint4*>(k_store + page_row(page, h, off, kv_heads, dim) + d) =
+            *reinterpret_cast<const uint4*>(k + h * dim + d);
+      }
+      for (int e = threadIdx.x; e < kv_heads * vdim / N; e += blockDim.x) {
+        const int h = e / (vdim / N), d = (e - h * (vdim / N)) * N;
+        *reinterpret_cast<uint4*>(v_store + page_row(page, h, off, kv_heads, vdim) + d) =
+            *reinterpret_cast<const uint4*>(v + h * vdim + d);
+      }
+    } else {
+      for (int e = threadIdx.x; e < kv_heads * dim; e += blockDim.x) {
+        const int h = e / dim, d = e - h * dim;
+        k_store[page_row(page, h, off, kv_heads, dim) + d] = k[e];
+      }
+      for (int e = threadIdx.x; e < kv_heads * vdim; e += blockDim.x) {
+        const int h = e / vdim, d = e - h * vdim;
+        v_store[page_row(page, h, off, kv_heads, vdim) + d] = v[e];
+      }
     }
     g_at += kv_heads * (dim + vdim);
   }
@@ -160,13 +176,17 @@ int sb_sink_prepare(int dtype, const void* proj, int proj_width, const int* tok_
                     int heads, int kv_heads, int dim, int vdim, int write, cudaStream_t s) {
   if (n_tokens == 0) return 0;
   if (proj_width < heads * dim + (write ? kv_heads * (dim + vdim) : 0) + (gate ? heads : 0)) return -2;
+  const int n = dtype == 0 ? 4 : 8;
+  const int vec = write && proj_width % n == 0 && dim % n == 0 && vdim % n == 0 &&
+                  (((uintptr_t)proj | (uintptr_t)k_store | (uintptr_t)v_store) & 15) == 0;
+  const int threads = write && vec && kv_heads * (dim + vdim) / n > 128 ? 256 : 128;
   if (dtype == 0)
-    return launch_dependent(sink_prepare_kernel<float>, dim3(n_tokens), dim3(128), 0, s, (const float*)proj, proj_width,
+    return launch_dependent(sink_prepare_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)proj, proj_width,
                             tok_pos, tok_slot, block_table, table_stride, (float*)k_store, (float*)v_store, gate, heads,
-                            kv_heads, dim, vdim, write);
-  return launch_dependent(sink_prepare_kernel<bf16>, dim3(n_tokens), dim3(128), 0, s, (const bf16*)proj, proj_width,
+                            kv_heads, dim, vdim, write, vec);
+  return launch_dependent(sink_prepare_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, (const bf16*)proj, proj_width,
                           tok_pos, tok_slot, block_table, table_stride, (bf16*)k_store, (bf16*)v_store, gate, heads,
-                          kv_heads, dim, vdim, write);
+                          kv_heads, dim, vdim, write, vec);
 }
 
 // q: rows of q_stride entries whose first heads * dim are the queries; out: [n_tokens, heads * vdim].

@@ -12,7 +12,12 @@
 //
 // Scores are kept in the base-2 domain: s = q.k * scale * log2(e) - r1 * log2(1 + r2 * (i - j)), since
 // ln(x) * log2(e) = log2(x); the sink enters as the state the running softmax starts from (maximum =
-// sink * log2(e), sum = 1).  Each row carries its own position, head, penalty, sink and gate.
+// sink * log2(e), sum = 1).  Each row carries its own position, head, sink and gate.  The penalty of a
+// page depends on the head and on i - j alone, and a block's rows and a page's keys span at most 127
+// distances: the block forms those values once per page and head in shared memory (a table of 128
+// entries a head, made while the page before is multiplied) instead of one logarithm per score.  Pages
+// that lie wholly inside what every row may see skip the mask; warps without a valid row (a single
+// token fills only `group` rows) skip the arithmetic and only help to copy.
 //
 // With n_splits > 1 the pages of a block are dealt out to gridDim.z blocks, which leave (maximum, sum,
 // accumulator) per row in scratch memory for sink_merge_kernel: for steps of few rows (single tokens).
@@ -72,6 +77,7 @@ sink_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   uint8_t* q_tile = sk_mem;                        // [64][D]
   uint8_t* k_tiles = sk_mem + SK_ROWS * D * 2;     // 2 x [64][D]
   uint8_t* v_tiles = k_tiles + 2 * K_BYTES;        // 2 x [64][DV]
+  float* pen_tab = reinterpret_cast<float*>(v_tiles + 2 * V_BYTES);   // [group][128], entry tok + 63 - key of the page
 
   // (no early launch_dependents: the successor starts when this kernel's blocks have exited)
   pdl_wait();
@@ -124,12 +130,27 @@ sink_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     for (int idx = tid; idx < SB_PAGE_TOKENS * CV; idx += SK_THREADS)
       sk_cp16(v_tiles + buf * V_BYTES + sk_offset<DV>(idx / CV, idx % CV), vs + (size_t)idx * 8);
   };
+  // the penalties of page t: entry [g][x] belongs to the distance pos0 - j0 - 63 + x (negative ones are masked)
+  auto make_penalties = [&](int t) {
+    if (!r1) return;
+    const int d0 = pos0 - (page_lo + t_begin + t) * SB_PAGE_TOKENS - 63;
+    for (int idx = tid; idx < group * 128; idx += SK_THREADS) {
+      const int g = idx >> 7, x = idx & 127;
+      const int head = kvh * group + g;
+      pen_tab[idx] = x < tokens_valid + 63 ? r1[head] * log2f(1.f + r2[head] * (float)max(d0 + x, 0)) : 0.f;
+    }
+  };
   if (n_tiles > 0) load_kv(0, 0);
   sk_commit();
   if (n_tiles > 1) load_kv(1, 1);
   sk_commit();
+  if (n_tiles > 0) make_penalties(0);
   sk_wait<1>();
   __syncthreads();
+  const bool warp_live = warp * 16 < rows_valid;
+  int lo_last = 0;                                 // the first key the block's last token may see
+  if (chunk > 0) lo_last = hi / chunk * chunk;
+  if (window > 0 && hi - window + 1 > lo_last) lo_last = hi - window + 1;
 
   // ---- this warp's 16 query rows as A fragments
   uint32_t qf[KSTEPS][4];
@@ -140,8 +161,8 @@ sink_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
       sk_ldm4(sk_smem(q_tile + sk_offset<D>(r, 2 * kk + (lane >> 4))), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
   }
   // ---- this thread's two rows: where they stand, which head they are, what they may see
-  int row_pos[2], row_lo[2], row_head[2];
-  float pen1[2], pen2[2], m_run[2], l_run[2];
+  int row_pos[2], row_lo[2], row_head[2], row_pen[2];
+  float m_run[2], l_run[2];
   bool row_ok[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -154,8 +175,7 @@ sink_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     if (chunk > 0) first = row_pos[h] / chunk * chunk;
     if (window > 0 && row_pos[h] - window + 1 > first) first = row_pos[h] - window + 1;
     row_lo[h] = first;
-    pen1[h] = r1 ? r1[row_head[h]] : 0.f;
-    pen2[h] = r1 ? r2[row_head[h]] : 0.f;
+    row_pen[h] = (rr % group) * 128 + rr / group + 63;
     const bool with_sink = sink != nullptr && split == 0;
     m_run[h] = with_sink ? sink[row_head[h]] * 1.4426950408889634f : -INFINITY;
     l_run[h] = with_sink && (lane & 3) == 0 ? 1.f : 0.f;      // the row's sum is spread over its four lanes
@@ -169,7 +189,7 @@ sink_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     const uint8_t* kt = k_tiles + buf * K_BYTES;
     const uint8_t* vt = v_tiles + buf * V_BYTES;
     const int j0 = (page_lo + t_begin + t) * SB_PAGE_TOKENS;
-
+    if (warp_live) {
     // S = Q K^T for 64 keys: 8 blocks of 8 keys
     float s[8][4];
 #pragma unroll
@@ -187,16 +207,17 @@ sink_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     }
 
     // scale, penalty, mask, online softmax
+    const bool edge = j0 + SB_PAGE_TOKENS - 1 > pos0 || j0 < lo_last;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int nb = 0; nb < 8; ++nb) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int h = e >> 1;
-        const int j = j0 + nb * 8 + (lane & 3) * 2 + (e & 1);
+        const int jj = nb * 8 + (lane & 3) * 2 + (e & 1);
         float v = s[nb][e] * scale_log2;
-        if (r1) v -= pen1[h] * __log2f(1.f + pen2[h] * (float)(row_pos[h] - j));
-        if (j > row_pos[h] || j < row_lo[h]) v = -INFINITY;
+        if (r1) v -= pen_tab[row_pen[h] - jj];
+        if (edge && (j0 + jj > row_pos[h] || j0 + jj < row_lo[h])) v = -INFINITY;
         s[nb][e] = v;
         mx[h] = fmaxf(mx[h], v);
       }
@@ -242,9 +263,12 @@ sink_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
         sk_mma(o[n + 1], pf[kk], b2, b3);
       }
     }
+    }  // warp_live
 
-    // this buffer is free: fetch the tile after next, then make sure the next one has landed
+    // this buffer and the penalties are free: fetch the tile after next, form the next page's penalties,
+    // then make sure the next tile has landed
     __syncthreads();
+    if (t + 1 < n_tiles) make_penalties(t + 1);
     if (t + 2 < n_tiles) load_kv(t + 2, buf);
     sk_commit();
     sk_wait<1>();
@@ -328,12 +352,12 @@ static int sk_launch(const void* q, int q_stride, void* out, float* part_acc, fl
   const int tokens_per_block = SK_ROWS / group;
   int subs = (SB_PAGE_TOKENS + tokens_per_block - 1) / tokens_per_block;
   if (max_q_len > 0) subs = min(subs, (min(max_q_len, SB_PAGE_TOKENS) + tokens_per_block - 1) / tokens_per_block);
-  const int smem = SK_ROWS * D * 2 + 2 * SB_PAGE_TOKENS * (D + DV) * 2;
-  static bool configured = false;
-  if (!configured) {
+  const int smem = SK_ROWS * D * 2 + 2 * SB_PAGE_TOKENS * (D + DV) * 2 + group * 128 * (int)sizeof(float);
+  static int configured = 0;
+  if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(sink_attention_tc_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured = smem;
   }
   int rc = launch_dependent(sink_attention_tc_kernel<D, DV>, dim3(n_tiles * subs, kv_heads, n_splits), dim3(SK_THREADS),
                             smem, s, (const bf16*)q, q_stride, (bf16*)out, part_acc, part_ml, (const bf16*)k_store,

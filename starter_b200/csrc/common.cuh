@@ -49,6 +49,14 @@ __device__ __forceinline__ uint32_t pack_exact_bf16(float lo, float hi) {
 // for results that are rounded to bfloat16 at once; the 32-bit path uses the exact ones.
 #define SB_ACT_SILU 1
 #define SB_ACT_GELU_TANH 2
+// 3: the clamped gate, g * sigmoid(1.702 g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit):
+// it combines gate and up itself (gate_clamped below) and needs the limit beside the code.
+#define SB_ACT_CLAMPED 3
+__device__ __forceinline__ float gate_clamped(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return __fdividef(g, 1.f + __expf(-1.702f * g)) * (u + 1.f);
+}
 __device__ __forceinline__ float gate_act_fast(float g, int act) {
   const float z = act == SB_ACT_GELU_TANH ? -1.5957691216057308f * (g + 0.044715f * g * g * g) : -g;
   return __fdividef(g, 1.f + __expf(z));

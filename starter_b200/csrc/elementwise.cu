@@ -364,7 +364,8 @@ __global__ void gated_clamped_kernel(const T* __restrict__ gu, T* __restrict__ a
     const int col = (int)(i - row * inner);
     const float g = fminf(to_f<T>(gu[row * 2 * inner + col]), limit);
     const float u = fminf(fmaxf(to_f<T>(gu[row * 2 * inner + inner + col]), -limit), limit);
-    act[i] = from_f<T>(g / (1.f + expf(-1.702f * g)) * (u + 1.f));
+    act[i] = from_f<T>(sizeof(T) == 2 ? __fdividef(g, 1.f + __expf(-1.702f * g)) * (u + 1.f)      // as the products' epilogue
+                                      : g / (1.f + expf(-1.702f * g)) * (u + 1.f));
   }
 }
 

@@ -115,6 +115,7 @@ struct PromptGemmArgs {
   int group_m;          // row tiles per group (see pg_tile)
   unsigned long long wait_limit_ns;
   int withhold_kblock;  // >= 0: the first CTA leaves out its weight copy of this k-block of its first tile
+  float limit;          // the clamp of the gated activation with code 3
 };
 
 // ------------------------------------------------------------------------------------------ kernel
@@ -310,7 +311,8 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float gr = rnd<bf16>(v[j]), ur = rnd<bf16>(u[j]);
-            v[j] = rnd<bf16>(args.gated == SB_ACT_GELU_TANH ? gate_act_fast(gr, SB_ACT_GELU_TANH) : gr / (1.f + __expf(-gr))) * ur;
+            if (args.gated == SB_ACT_CLAMPED) v[j] = gate_clamped(gr, ur, args.limit);
+            else v[j] = rnd<bf16>(args.gated == SB_ACT_GELU_TANH ? gate_act_fast(gr, SB_ACT_GELU_TANH) : gr / (1.f + __expf(-gr))) * ur;
           }
         }
         if (c == n_chunks - 1) {
@@ -361,7 +363,7 @@ static int pg_launch(const CUtensorMap& map_x, const CUtensorMap& map_w, const P
 // pairs.  Returns -2 for sizes it does not take, -3/-4 if the tensor maps cannot be made.
 static int pg_entry(const void* x, const void* w, void* out, const void* residual, int rows, int n_out, int k_dim, int bn, int pairs,
                     int gated, int* status, unsigned long long wait_limit_ns, int withhold_kblock,
-                    cudaStream_t s) {
+                    cudaStream_t s, float limit = 0.f) {
   if (rows == 0 || n_out == 0) return 0;
   if (k_dim % 8 || k_dim <= 0) return -2;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return -2;
@@ -410,6 +412,7 @@ static int pg_entry(const void* x, const void* w, void* out, const void* residua
   if (group_m > m_tiles) group_m = m_tiles;
   args.group_m = (int)group_m;
   args.wait_limit_ns = wait_limit_ns; args.withhold_kblock = withhold_kblock;
+  args.limit = limit;
   const int smem = stages * stage_bytes + 1024;
   return gated ? pg_launch<true>(map_x, map_w, args, pairs, smem, s)
                : pg_launch<false>(map_x, map_w, args, pairs, smem, s);
@@ -420,6 +423,13 @@ extern "C" {
 int sb_gemm_prompt(const void* x, const void* w, void* out, const void* residual, int rows, int n_out, int k_dim, int bn, int pairs,
                    int gated, int* status, cudaStream_t s) {
   return pg_entry(x, w, out, residual, rows, n_out, k_dim, bn, pairs, gated, status, TC_WAIT_LIMIT_NS, -1, s);
+}
+
+// The gated product with the clamped activation (code 3): g * sigmoid(1.702 g) * (u + 1) with g = min(gate,
+// limit), u = clamp(up, -limit, limit), gate and up rounded to bfloat16 first.
+int sb_gemm_prompt_clamped(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, int bn, int pairs,
+                           float limit, int* status, cudaStream_t s) {
+  return pg_entry(x, w, out, nullptr, rows, n_out, k_dim, bn, pairs, SB_ACT_CLAMPED, status, TC_WAIT_LIMIT_NS, -1, s, limit);
 }
 
 // The same product with one weight copy left out on purpose (k-block `withhold_kblock` of the first

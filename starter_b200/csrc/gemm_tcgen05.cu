@@ -74,6 +74,7 @@ struct GemmArgs {
   int splits, stages, gated, out_float;
   unsigned long long wait_limit_ns;   // how long a wait may take before the CTA gives up
   int withhold_stage;                 // >= 0: the activation copy of this k-block is left out (tests)
+  float limit;                        // the clamp of the gated activation with code 3
 };
 
 template <int BM, bool GATED>
@@ -268,7 +269,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float gr = rnd<bf16>(g[j]), ur = rnd<bf16>(u[j]);
-            g[j] = rnd<bf16>(args.gated == SB_ACT_GELU_TANH ? gate_act_fast(gr, SB_ACT_GELU_TANH) : gr / (1.f + __expf(-gr))) * ur;
+            if (args.gated == SB_ACT_CLAMPED) g[j] = gate_clamped(gr, ur, args.limit);
+            else g[j] = rnd<bf16>(args.gated == SB_ACT_GELU_TANH ? gate_act_fast(gr, SB_ACT_GELU_TANH) : gr / (1.f + __expf(-gr))) * ur;
           }
         }
         const int ncol = (GATED ? tile * 64 : tile * TILE_N) + orow;
@@ -331,7 +333,7 @@ extern "C" {
 // Returns -2 for sizes it does not take, -3/-4 if the tensor maps cannot be made.
 static int gemm_entry(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, int bm,
                       int splits, int stages, int gated, int out_float, int* status,
-                      unsigned long long wait_limit_ns, int withhold_stage, cudaStream_t s) {
+                      unsigned long long wait_limit_ns, int withhold_stage, cudaStream_t s, float limit = 0.f) {
   if (rows == 0 || n_out == 0) return 0;
   if (k_dim % 8 || k_dim <= 0 || splits < 1 || splits > GEMM_MAX_SPLITS) return -2;
   if (stages < 2 || stages > GEMM_MAX_STAGES) return -2;
@@ -350,6 +352,7 @@ static int gemm_entry(const void* x, const void* w, void* out, int rows, int n_o
   args.rows = rows; args.n_out = n_out; args.k_dim = k_dim;
   args.splits = splits; args.stages = stages; args.gated = gated; args.out_float = out_float;
   args.wait_limit_ns = wait_limit_ns; args.withhold_stage = withhold_stage;
+  args.limit = limit;
 #define BY_TILE(G)                                                           \
   switch (bm) {                                                              \
     case 16: return launch<16, G>(map_w, map_x, args, tiles, m_tiles, s);    \
@@ -370,6 +373,14 @@ int sb_gemm_tcgen05(const void* x, const void* w, void* out, int rows, int n_out
                     int splits, int stages, int gated, int out_float, int* status, cudaStream_t s) {
   return gemm_entry(x, w, out, rows, n_out, k_dim, bm, splits, stages, gated, out_float, status,
                     WAIT_LIMIT_NS, -1, s);
+}
+
+// The gated product with the clamped activation (code 3): w is [gate; up], the result g * sigmoid(1.702 g) *
+// (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), gate and up rounded to bfloat16 first.
+int sb_gemm_tcgen05_clamped(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, int bm,
+                            int splits, int stages, float limit, int* status, cudaStream_t s) {
+  return gemm_entry(x, w, out, rows, n_out, k_dim, bm, splits, stages, SB_ACT_CLAMPED, 0, status, WAIT_LIMIT_NS, -1, s,
+                    limit);
 }
 
 // The same product with one activation copy left out on purpose (k-block `withhold_stage` of every

@@ -1897,5 +1897,29 @@ def sink_attention_step(q, k_store, v_store, block_table, ctx, heads, kv_heads, 
 
 def linear_gated_clamped(x, weight, limit, status=None):
     """``g * sigmoid(1.702 g) * (u + 1)`` with ``g = min(x @ gate.T, limit)`` and ``u = clamp(x @ up.T, -limit,
-    limit)`` for ``weight = [gate; up]`` stacked (``[2 * I, K]``); returns ``[T, I]``."""
+    limit)`` for ``weight = [gate; up]`` stacked (``[2 * I, K]``); returns ``[T, I]``.  In bfloat16 the
+    activation is the epilogue of the tensor-core products (few rows; 512 rows and more) where they take the
+    operands; elsewhere the product is followed by ``gated_clamped``."""
+    _need(x, "x", None, 2)
+    _need(weight, "weight", x.dtype, 2)
+    rows, k_dim = x.shape
+    n_total = weight.shape[0]
+    if weight.shape[1] != k_dim or n_total % 2:
+        raise KernelError(f"weight {tuple(weight.shape)} is no stacked [gate; up] for inputs of width {k_dim}")
+    n_out = n_total // 2
+    fused = x.dtype == torch.bfloat16 and rows > 0 and tensor_core_ok(x, weight, True, n_out)
+    if fused and rows <= TENSOR_CORE_MAX_ROWS:
+        bm, splits, stages = gemm_plan(rows, n_out, k_dim, True)
+        stages = min(max(stages, -(-bm * 512 // (16384 + bm * 128))), (226 * 1024) // (16384 + bm * 128))
+        out = torch.empty((rows, n_out), dtype=torch.bfloat16, device=x.device)
+        rc = _lib("gemm_tcgen05").sb_gemm_tcgen05_clamped(_ptr(x), _ptr(weight), _ptr(out), rows, n_out, k_dim, bm, splits,
+                                                          stages, ctypes.c_float(limit), _ptr(status), _stream())
+        _check(rc, "gemm_tcgen05 (clamped gate)")
+        return out
+    if fused and rows >= PROMPT_MIN_ROWS:
+        out = torch.empty((rows, n_out), dtype=torch.bfloat16, device=x.device)
+        rc = _lib("gemm_prompt_tcgen05").sb_gemm_prompt_clamped(_ptr(x), _ptr(weight), _ptr(out), rows, n_out, k_dim, 0, 0,
+                                                                ctypes.c_float(limit), _ptr(status), _stream())
+        _check(rc, "gemm_prompt_tcgen05 (clamped gate)")
+        return out
     return gated_clamped(linear(x, weight, status=status), limit)

@@ -166,6 +166,27 @@ def test_cap_and_clamped_gate_alone(dtype):
     close(got, a * torch.sigmoid(1.702 * a) * (b + 1.0), dtype, "the clamped gate", bf16=5e-3)
 
 
+@pytest.mark.parametrize("rows", [1, 8, 40, 128, 200, 512, 700])
+@pytest.mark.parametrize("width, inner, limit", [(256, 192, 0.9), (128, 64, 2.0), (136, 72, 1.0)])
+def test_clamped_gated_product_fused_and_not(rows, width, inner, limit):
+    """The activation inside the tensor-core products' epilogues (few rows; 512 and more) and behind a plain
+    product (in between, and sizes the tensor-core products refuse): all against the plain statement."""
+    from starter_b200 import ops
+
+    g = torch.Generator().manual_seed(rows + inner)
+    x = dev(torch.randn(rows, width, generator=g, dtype=F), torch.bfloat16)
+    w = dev(torch.randn(2 * inner, width, generator=g, dtype=F) * 0.12, torch.bfloat16)     # many entries past the limits
+    got = ops.linear_gated_clamped(x, w, limit)
+    gu = (x.double().cpu() @ w.double().cpu().T).to(torch.bfloat16).double()
+    a, b = gu[:, :inner].clamp(max=limit), gu[:, inner:].clamp(-limit, limit)
+    close(got, a * torch.sigmoid(1.702 * a) * (b + 1.0), "bfloat16", f"{rows} rows", bf16=1.2e-2)
+    x32, w32 = x.float(), w.float()
+    got = ops.linear_gated_clamped(x32, w32, limit)
+    gu = x32.double().cpu() @ w32.double().cpu().T
+    a, b = gu[:, :inner].clamp(max=limit), gu[:, inner:].clamp(-limit, limit)
+    close(got, a * torch.sigmoid(1.702 * a) * (b + 1.0), "float32", f"{rows} rows, float32", fp32=1e-5)
+
+
 def paged(k, v, t, pages=(5, 2, 7, 0, 3)):
     """Keys ``[T, G, D]`` and values ``[T, G, Dv]`` of one sequence filed in scattered pages of slot 1."""
     n, kv_heads, dim = k.shape
