@@ -24,6 +24,13 @@
 // that continues a sequence needs nothing special: a query at absolute position p sees keys j <= p
 // (engine/engine.py:781-787) and, with a window w, j > p - w.
 //
+// The same kernel also serves attention whose positions enter through the scores and the mask (EXT, see
+// attention_sink.cu): the penalty r1 log2(1 + r2 (p - j)) is taken off a score as it leaves tensor
+// memory (S is unscaled there, so the penalty is divided by the scale first); a row masks the keys
+// before its own chunk; the sink is the state a row's softmax starts from (reference = sink log2(e),
+// sum = 1); the gate multiplies the row's result.  The queries may lie at the front of wider rows
+// (a stacked projection): the tensor map of Q covers those rows.
+//
 // Every wait on an mbarrier gives up after WAIT_LIMIT_NS, raises bit 16 of *status and lets the
 // block drain its copies, free its tensor memory and return.
 #include <cuda.h>
@@ -204,7 +211,17 @@ __device__ __forceinline__ uint32_t instr_desc(int n, int b_mn_major) {
          ((uint32_t)(TC_BQ >> 4) << 24);
 }
 
-template <int D>
+// What the EXT instance takes besides: r1, r2 (float [heads], both or neither), sink (float [heads] or null),
+// gate (float [tokens, heads] or null), chunk (0: none).
+struct TcExtras {
+  const float* r1;
+  const float* r2;
+  const float* sink;
+  const float* gate;
+  int chunk;
+};
+
+template <int D, bool EXT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
@@ -212,7 +229,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ seq_slot, const int* __restrict__ seq_q_start,
                             const int* __restrict__ seq_q_len, const int* __restrict__ seq_kv_len,
                             const int* __restrict__ tile_seq, const int* __restrict__ tile_first,
-                            int heads, int kv_heads, float scale_log2, int window, int* status, int list_of_blocks) {
+                            int heads, int kv_heads, float scale_log2, int window, int* status, int list_of_blocks,
+                            TcExtras ex) {
   constexpr int DC = D / 64;                        // 64-element (128-byte) chunks of the head
   constexpr int SUB = 128 * 128;                    // bytes of a [128 rows x 128 bytes] sub-tile
   constexpr int Q_BYTES = DC * SUB;                 // one tile of 128 queries
@@ -245,6 +263,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int hi = pos0 + rows_valid - 1;
   int lo = 0;
   if (window > 0 && pos0 - window + 1 > 0) lo = pos0 - window + 1;
+  if (EXT && ex.chunk > 0 && pos0 / ex.chunk * ex.chunk > lo) lo = pos0 / ex.chunk * ex.chunk;
   const int page_lo = lo / SB_PAGE_TOKENS, page_hi = hi / SB_PAGE_TOKENS;
   // steps of two pages (128 keys) that each tile of 128 queries needs, counted from page_lo
   int n_tile[2];
@@ -403,6 +422,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint8_t* p_row = p_sm + t * P_BYTES + r * 128;
     const int n_mine = n_tile[t];
     float m_ref = -INFINITY, l_run = 0.f;
+    // EXT: the first key of the row's own chunk, the first key of the chunk of the tile's last row, the
+    // penalty's two numbers (the first over the scale, because S is scaled after it), the sink
+    int row_lo = 0, tile_lo = 0;
+    float pen1 = 0.f, pen2 = 0.f;
+    if (EXT) {
+      if (ex.chunk > 0) {
+        row_lo = pos / ex.chunk * ex.chunk;
+        tile_lo = (pos0 + t * TC_BQ + TC_BQ - 1) / ex.chunk * ex.chunk;
+      }
+      if (ex.r1) {
+        pen1 = ex.r1[head] / scale_log2;
+        pen2 = ex.r2[head];
+      }
+      if (ex.sink) {
+        m_ref = ex.sink[head] * 1.4426950408889634f;
+        l_run = 1.f;
+      }
+    }
     pdl_wait();
     bool ok = true;
     for (int i = 0; i < n_mine && ok; ++i) {
@@ -411,7 +448,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int j0 = (page_lo + 2 * i) * SB_PAGE_TOKENS;
       const bool edge = j0 + TC_BK - 1 > pos0 + t * TC_BQ ||
-                        (window > 0 && j0 <= pos0 + t * TC_BQ + TC_BQ - window);
+                        (window > 0 && j0 <= pos0 + t * TC_BQ + TC_BQ - window) || (EXT && j0 < tile_lo);
       float sv[64];
       uint32_t pk[32];
       float mx = -INFINITY, rs = 0.f, rs_hi = 0.f;   // the row sum in two halves (packed adds)
@@ -419,11 +456,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // half h of the row of S from tensor memory, masked where the step touches an edge
       auto load_half = [&](int h) {
         tmem_load64(tmem_s + h * 64, sv);
+        if (EXT && ex.r1) {
+          const float far = (float)(pos - j0 - h * 64);       // the distance to this half's first key
+#pragma unroll
+          for (int e = 0; e < 64; ++e)
+            sv[e] -= pen1 * __log2f(fmaf(pen2, fmaxf(far - (float)e, 0.f), 1.f));
+        }
         if (edge) {
 #pragma unroll
           for (int e = 0; e < 64; ++e) {
             const int j = j0 + h * 64 + e;
-            if (j > pos || (window > 0 && j <= pos - window)) sv[e] = -INFINITY;
+            if (j > pos || (window > 0 && j <= pos - window) || (EXT && j < row_lo)) sv[e] = -INFINITY;
           }
         }
       };
@@ -520,8 +563,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (ok && n_mine > 0) ok = mbar_wait(&o_ready[t], (n_mine - 1) & 1, abort);
     if (ok && n_mine > 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float inv = 1.f / l_run;
       const bool valid = t * TC_BQ + r < rows_valid;
+      float inv = 1.f / l_run;
+      if (EXT && ex.gate && valid)
+        inv *= ex.gate[((size_t)seq_q_start[seq] + q_first + t * TC_BQ + r) * heads + head];
       bf16* dst = out + ((size_t)seq_q_start[seq] + q_first + t * TC_BQ + r) * ((size_t)heads * D) + (size_t)head * D;
 #pragma unroll 1
       for (int c = 0; c < D; c += 32) {
@@ -555,24 +600,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
 // ------------------------------------------------------------------------------------------ host
 
-template <int D>
+template <int D, bool EXT>
 static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out,
                   const int* block_table, int table_stride, const int* seq_slot, const int* seq_q_start,
                   const int* seq_q_len, const int* seq_kv_len, const int* tile_seq, const int* tile_first,
                   int n_tiles, int heads, int kv_heads, float scale, int window, int* status, int list_of_blocks,
-                  cudaStream_t s) {
+                  cudaStream_t s, TcExtras ex = TcExtras{nullptr, nullptr, nullptr, nullptr, 0}) {
   constexpr int DC = D / 64;
   const int smem = (2 * DC + 4 + TC_RING * DC) * 128 * 128 + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return launch_dependent(attention_prefill_tc_kernel<D>, dim3(heads, n_tiles), dim3(TC_THREADS), smem, s, mq, mk,
+  return launch_dependent(attention_prefill_tc_kernel<D, EXT>, dim3(heads, n_tiles), dim3(TC_THREADS), smem, s, mq, mk,
                           mv, (bf16*)out, block_table, table_stride, seq_slot, seq_q_start, seq_q_len, seq_kv_len,
                           tile_seq, tile_first, heads, kv_heads, scale * 1.4426950408889634f, window, status,
-                          list_of_blocks);
+                          list_of_blocks, ex);
 }
 
 static unsigned long long next_limit_ns = WAIT_LIMIT_NS;
@@ -618,7 +663,7 @@ int sb_attention_prefill_tc(const void* q, void* out, const void* k_store, const
     cudaMemcpyToSymbolAsync(tc_wait_limit_ns, &next_limit_ns, sizeof(next_limit_ns), 0, cudaMemcpyHostToDevice, s);
     cudaStreamSynchronize(s);
   }
-  rc = head_dim == 64 ? launch<64>(ARGS) : launch<128>(ARGS);
+  rc = head_dim == 64 ? launch<64, false>(ARGS) : launch<128, false>(ARGS);
   if (test_run) {
     cudaStreamSynchronize(s);
     next_withhold_step = -1;
@@ -629,6 +674,36 @@ int sb_attention_prefill_tc(const void* q, void* out, const void* k_store, const
   }
   return rc;
 #undef ARGS
+}
+
+// The same for attention with a distance penalty, chunks, a sink and head gates (see attention_sink.cu): q
+// points at rows of q_width entries (a multiple of 8) whose first heads * head_dim are the queries; out is
+// [n_tokens, heads * head_dim]; keys and values both have head_dim entries (64 or 128); scale > 0.
+int sb_sink_attention_tcgen05(const void* q, int q_width, void* out, const void* k_store, const void* v_store,
+                              const int* block_table, int table_stride, const int* seq_slot, const int* seq_q_start,
+                              const int* seq_q_len, const int* seq_kv_len, const int* tile_seq, const int* tile_first,
+                              int n_tiles, int n_tokens, int n_pages, int heads, int kv_heads, int head_dim, float scale,
+                              const float* r1, const float* r2, const float* sink, const float* gate, int chunk, int window,
+                              int* status, int list_of_blocks, cudaStream_t s) {
+  if (n_tiles == 0) return 0;
+  if (kv_heads <= 0 || heads % kv_heads || !(scale > 0.f)) return -2;
+  if (head_dim != 64 && head_dim != 128) return -2;
+  if ((r1 == nullptr) != (r2 == nullptr) || q_width % 8 || q_width < heads * head_dim) return -2;
+  if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_store | (uintptr_t)v_store) & 15) return -2;
+  CUtensorMap mq, mk, mv;
+  int rc = sb_make_map(&mq, q, n_tokens, q_width, TC_BQ);
+  if (rc) return rc;
+  const long long kv_rows = (long long)n_pages * kv_heads * SB_PAGE_TOKENS;
+  rc = sb_make_map(&mk, k_store, kv_rows, head_dim, SB_PAGE_TOKENS);
+  if (rc) return rc;
+  rc = sb_make_map(&mv, v_store, kv_rows, head_dim, SB_PAGE_TOKENS);
+  if (rc) return rc;
+  const TcExtras ex{r1, r2, sink, gate, chunk > 0 ? chunk : 0};
+  if (head_dim == 64)
+    return launch<64, true>(mq, mk, mv, out, block_table, table_stride, seq_slot, seq_q_start, seq_q_len, seq_kv_len,
+                            tile_seq, tile_first, n_tiles, heads, kv_heads, scale, window, status, list_of_blocks, s, ex);
+  return launch<128, true>(mq, mk, mv, out, block_table, table_stride, seq_slot, seq_q_start, seq_q_len, seq_kv_len,
+                           tile_seq, tile_first, n_tiles, heads, kv_heads, scale, window, status, list_of_blocks, s, ex);
 }
 
 }  // extern "C"

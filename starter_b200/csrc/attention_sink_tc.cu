@@ -88,8 +88,9 @@ sink_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   SB_BEHIND_WAIT(seq_q_len);
   SB_BEHIND_WAIT(seq_kv_len);
   SB_BEHIND_WAIT(block_table);
-  const int tile = blockIdx.x / subs, sub = blockIdx.x - tile * subs;
-  const int kvh = blockIdx.y;
+  // key/value heads run fastest: the work list names the tiles with most keys first, and so do the blocks
+  const int kvh = blockIdx.x % kv_heads, ts = blockIdx.x / kv_heads;
+  const int tile = ts / subs, sub = ts - tile * subs;
   const int split = blockIdx.z, n_splits = gridDim.z;
   const int group = heads / kv_heads;
   const int seq = tile_seq[tile];
@@ -359,7 +360,7 @@ static int sk_launch(const void* q, int q_stride, void* out, float* part_acc, fl
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  int rc = launch_dependent(sink_attention_tc_kernel<D, DV>, dim3(n_tiles * subs, kv_heads, n_splits), dim3(SK_THREADS),
+  int rc = launch_dependent(sink_attention_tc_kernel<D, DV>, dim3(n_tiles * subs * kv_heads, 1, n_splits), dim3(SK_THREADS),
                             smem, s, (const bf16*)q, q_stride, (bf16*)out, part_acc, part_ml, (const bf16*)k_store,
                             (const bf16*)v_store, block_table, table_stride, seq_slot, seq_q_start, seq_q_len, seq_kv_len,
                             tile_seq, tile_first, r1, r2, sink, gate, n_tokens, heads, kv_heads, subs, tokens_per_block,

@@ -1882,10 +1882,54 @@ def sink_attention_tc(q, k_store, v_store, block_table, seq_slot, seq_q_start, s
     return out
 
 
+def sink_tcgen05_takes(q, dim, vdim) -> bool:
+    """Whether the tcgen05 prompt kernel takes these operands: bfloat16, keys and values of one size, 64 or
+    128, query rows that are a multiple of 8 wide and start on 16-byte boundaries."""
+    return (q.dtype == torch.bfloat16 and dim == vdim and dim in PREFILL_TC_HEAD_DIMS and q.shape[1] % 8 == 0
+            and q.data_ptr() % 16 == 0)
+
+
+def sink_attention_tcgen05(q, k_store, v_store, block_table, seq_slot, seq_q_start, seq_q_len, seq_kv_len, tile_seq,
+                           tile_first, heads, kv_heads, dim, scale, penalty=None, sink=None, gate=None, chunk=None,
+                           window=None, status=None, blocks=None):
+    """``sink_attention`` for prompts on the tcgen05 kernel of ``attention_prefill`` (256 queries of a head a
+    block, S and O in tensor memory), which takes the penalty, the chunks, the sink and the gate as extras.
+    ``blocks = (block_seq, block_first)``: the work list in blocks of 256 queries (else the tiles of 64 are
+    launched and three of four blocks find nothing to do)."""
+    r1, r2 = _sink_check(q, k_store, v_store, heads, kv_heads, dim, dim, penalty, sink, gate)
+    if not sink_tcgen05_takes(q, dim, dim):
+        raise KernelError(f"the tcgen05 attention takes bfloat16 heads of 64 or 128 entries, keys and values alike, in "
+                          f"rows that are multiples of 8 wide; got {q.dtype}, {dim}, rows of {q.shape[1]}")
+    if not scale > 0:
+        raise KernelError("the tcgen05 attention needs a positive scale")
+    _need(block_table, "block_table", torch.int32, 2)
+    for name, t in (("seq_slot", seq_slot), ("seq_q_start", seq_q_start), ("seq_q_len", seq_q_len),
+                    ("seq_kv_len", seq_kv_len), ("tile_seq", tile_seq), ("tile_first", tile_first)):
+        _need(t, name, torch.int32, 1)
+    own_list = blocks is not None and blocks[0] is not None
+    if own_list:
+        for name, t in (("block_seq", blocks[0]), ("block_first", blocks[1])):
+            _need(t, name, torch.int32, 1)
+    list_seq, list_first = blocks if own_list else (tile_seq, tile_first)
+    out = torch.empty((q.shape[0], heads * dim), dtype=q.dtype, device=q.device)
+    rc = _lib("attention_prefill_tc").sb_sink_attention_tcgen05(
+        _ptr(q), q.shape[1], _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table), block_table.shape[1],
+        _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(list_seq), _ptr(list_first),
+        list_seq.shape[0], q.shape[0], k_store.shape[0], heads, kv_heads, dim, ctypes.c_float(scale), _ptr(r1), _ptr(r2),
+        _ptr(sink), _ptr(gate), int(chunk or 0), int(window or 0), _ptr(status), int(own_list), _stream())
+    _check(rc, "sink_attention_tcgen05")
+    return out
+
+
 def sink_attention_step(q, k_store, v_store, block_table, ctx, heads, kv_heads, dim, vdim, scale, penalty=None,
                         sink=None, gate=None, chunk=None, window=None):
-    """``sink_attention`` for the step ``ctx`` describes, on the kernel that fits its shape: tensor cores for
-    bfloat16 at sizes they take, the plain kernel otherwise (float32, other sizes)."""
+    """``sink_attention`` for the step ``ctx`` describes, on the kernel that fits its shape: for bfloat16 the
+    tcgen05 kernel when a sequence brings more than 128 tokens and keys and values have 64 or 128 entries, the
+    mma.sync kernel for other steps and sizes it takes; the plain kernel otherwise (float32, other sizes)."""
+    if ctx.max_q_len > 128 and scale > 0 and sink_tcgen05_takes(q, dim, vdim):
+        return sink_attention_tcgen05(q, k_store, v_store, block_table, ctx.seq_slot, ctx.seq_q_start, ctx.seq_q_len,
+                                      ctx.seq_kv_len, ctx.tile_seq, ctx.tile_first, heads, kv_heads, dim, scale, penalty,
+                                      sink, gate, chunk, window, ctx.status, (ctx.block_seq, ctx.block_first))
     if sink_tc_takes(q, heads, kv_heads, dim, vdim):
         splits = sink_splits(ctx.n_seqs, kv_heads, chunk, window, ctx.max_kv_len) if ctx.max_q_len == 1 else 1
         return sink_attention_tc(q, k_store, v_store, block_table, ctx.seq_slot, ctx.seq_q_start, ctx.seq_q_len,

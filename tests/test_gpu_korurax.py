@@ -209,7 +209,8 @@ def paged(k, v, t, pages=(5, 2, 7, 0, 3)):
     (4, 2, 16, 32, 10, None, "psg"), (6, 1, 24, 40, 3, None, "psg"), (4, 2, 32, 64, 64, None, "psg"),
     (6, 2, 64, 32, 100, None, "psg"), (8, 1, 16, 16, 130, None, "psg"), (2, 2, 128, 128, 65, None, "psg"),
     (3, 3, 64, 64, None, None, "s"), (4, 1, 32, 32, None, 70, "p"), (2, 1, 64, 16, 128, 33, "g"),
-    (5, 5, 16, 64, 1000, None, ""), (4, 4, 8, 8, 1, None, "psg")])
+    (5, 5, 16, 64, 1000, None, ""), (4, 4, 8, 8, 1, None, "psg"), (4, 2, 64, 64, 100, None, "psg"),
+    (2, 1, 128, 128, None, 90, "pg"), (2, 2, 64, 64, 200, 150, "")])
 def test_attention_alone_with_one_key_that_stands_out(heads, kv_heads, dim, vdim, chunk, window, extras, dtype):
     """Queries late in a sequence of 300 (five scattered pages) score one key far above the rest: the first
     key of the query's chunk and the key just before it, keys on either side of a page border, the query's
@@ -275,6 +276,23 @@ def test_attention_alone_with_one_key_that_stands_out(heads, kv_heads, dim, vdim
                                     ints([0]), ints([0]), heads, kv_heads, dim, vdim, scale, pen, sk,
                                     gt[299:].contiguous() if gt is not None else None, chunk, window, n_splits=parts)
         close(out, want[299:], dtype, f"tensor cores, one token in {parts} parts")
+    if not ops.sink_tcgen05_takes(q2, dim, vdim):
+        return
+    # the tcgen05 kernel: blocks of 256 queries (one full, one of 44), from the list of blocks and from the
+    # list of tiles; then a later portion of 170 tokens
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for blocks in ((ints([0, 0]), ints([0, 256])), None):
+        out = ops.sink_attention_tcgen05(q2, ks, vs, table, ints([1]), ints([0]), ints([n]), ints([n]), ints([0, 0, 0, 0, 0]),
+                                         ints([128, 0, 256, 192, 64]), heads, kv_heads, dim, scale, pen, sk, gt, chunk, window,
+                                         status, blocks)
+        close(out, want, dtype, "tcgen05, whole")
+    late = torch.arange(130, 300, device="cuda")
+    out = ops.sink_attention_tcgen05(q2[late].contiguous(), ks, vs, table, ints([1]), ints([0]), ints([170]), ints([n]),
+                                     ints([0, 0, 0]), ints([0, 64, 128]), heads, kv_heads, dim, scale, pen, sk,
+                                     gt[late].contiguous() if gt is not None else None, chunk, window, status,
+                                     (ints([0]), ints([0])))
+    close(out, want[130:], dtype, "tcgen05, a later portion")
+    assert int(status.item()) == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -44,11 +44,12 @@ R_B = dict(architecture="Korurax", vocab=131, width=96, norm=dict(eps=1e-6), res
     attention(2, 1, 32, 16, 0.18, 65, moe(4, 2, 16, 1.5)),
 ])
 
-# sizes the tensor-core tiles take; three and eight query heads a key/value head; chunks of 64, 100 and 130
+# sizes the tensor-core tiles take (the second attention layer's also the tcgen05 prompt kernel's); three and
+# eight query heads a key/value head; chunks of 64, 100 and 130
 R_C = dict(architecture="Korurax", vocab=257, width=128, norm=dict(eps=1e-5), residual_mult=0.25, logit_softcap=12.0, layers=[
     attention(4, 2, 32, 64, 0.18, 64, dense(192, 2.0)),
     latent(4, 32, 32, 32, 64, 64, 0.125, 10000.0, moe(8, 2, 64, 2.5)),
-    attention(6, 2, 64, 32, 0.125, 100, moe(8, 3, 32, 1.0)),
+    attention(6, 2, 64, 64, 0.125, 100, moe(8, 3, 32, 1.0)),
     attention(8, 1, 16, 16, 0.25, 130, dense(64, 1.0)),
 ])
 
