@@ -19,6 +19,12 @@
 // that lie wholly inside what every row may see skip the mask; warps without a valid row (a single
 // token fills only `group` rows) skip the arithmetic and only help to copy.
 //
+// A block with at most 16 valid rows (a single token of up to 16 query heads a key/value head) would leave
+// three of its four warps idle and the fourth with a page's whole chain of products.  There the warps share
+// the KEYS instead: all four hold the same 16 rows, warp w takes keys 16w .. 16w + 15 of every page with a
+// running softmax of its own, and the four (maximum, sum, accumulator) are joined through shared memory
+// at the end.
+//
 // With n_splits > 1 the pages of a block are dealt out to gridDim.z blocks, which leave (maximum, sum,
 // accumulator) per row in scratch memory for sink_merge_kernel: for steps of few rows (single tokens).
 // The sink belongs to the first part alone.
@@ -78,6 +84,7 @@ sink_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   uint8_t* k_tiles = sk_mem + SK_ROWS * D * 2;     // 2 x [64][D]
   uint8_t* v_tiles = k_tiles + 2 * K_BYTES;        // 2 x [64][DV]
   float* pen_tab = reinterpret_cast<float*>(v_tiles + 2 * V_BYTES);   // [group][128], entry tok + 63 - key of the page
+  float* pen_coef = pen_tab + (heads / kv_heads) * 128;               // [group][2]: r1 and r2 of the block's heads
 
   // (no early launch_dependents: the successor starts when this kernel's blocks have exited)
   pdl_wait();
@@ -132,14 +139,13 @@ sink_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
       sk_cp16(v_tiles + buf * V_BYTES + sk_offset<DV>(idx / CV, idx % CV), vs + (size_t)idx * 8);
   };
   // the penalties of page t: entry [g][x] belongs to the distance pos0 - j0 - 63 + x (negative ones are masked)
+  // (thread x forms entry x of every head's table: 128 threads, 128 entries)
+  if (r1 && tid < 2 * group) pen_coef[tid] = (tid & 1) ? r2[kvh * group + (tid >> 1)] : r1[kvh * group + (tid >> 1)];
+  if (r1) __syncthreads();
   auto make_penalties = [&](int t) {
-    if (!r1) return;
-    const int d0 = pos0 - (page_lo + t_begin + t) * SB_PAGE_TOKENS - 63;
-    for (int idx = tid; idx < group * 128; idx += SK_THREADS) {
-      const int g = idx >> 7, x = idx & 127;
-      const int head = kvh * group + g;
-      pen_tab[idx] = x < tokens_valid + 63 ? r1[head] * log2f(1.f + r2[head] * (float)max(d0 + x, 0)) : 0.f;
-    }
+    if (!r1 || tid >= tokens_valid + 63) return;
+    const float d = (float)max(pos0 - (page_lo + t_begin + t) * SB_PAGE_TOKENS - 63 + tid, 0);
+    for (int g = 0; g < group; ++g) pen_tab[g * 128 + tid] = pen_coef[2 * g] * __log2f(fmaf(pen_coef[2 * g + 1], d, 1.f));
   };
   if (n_tiles > 0) load_kv(0, 0);
   sk_commit();
@@ -148,15 +154,17 @@ sink_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   if (n_tiles > 0) make_penalties(0);
   sk_wait<1>();
   __syncthreads();
-  const bool warp_live = warp * 16 < rows_valid;
+  const bool warp_live = rows_valid <= 16 || warp * 16 < rows_valid;
   int lo_last = 0;                                 // the first key the block's last token may see
   if (chunk > 0) lo_last = hi / chunk * chunk;
   if (window > 0 && hi - window + 1 > lo_last) lo_last = hi - window + 1;
 
-  // ---- this warp's 16 query rows as A fragments
+  // ---- this warp's 16 query rows as A fragments (with shared keys: every warp the first 16)
+  const bool share_keys = rows_valid <= 16;
+  const int row_base = share_keys ? 0 : warp * 16;
   uint32_t qf[KSTEPS][4];
   {
-    const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int r = row_base + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
     for (int kk = 0; kk < KSTEPS; ++kk)
       sk_ldm4(sk_smem(q_tile + sk_offset<D>(r, 2 * kk + (lane >> 4))), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
@@ -167,7 +175,7 @@ sink_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   bool row_ok[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const int r = warp * 16 + (lane >> 2) + 8 * h;
+    const int r = row_base + (lane >> 2) + 8 * h;
     row_ok[h] = r < rows_valid;
     const int rr = min(r, rows_valid - 1);
     row_pos[h] = pos0 + rr / group;
@@ -177,7 +185,7 @@ sink_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     if (window > 0 && row_pos[h] - window + 1 > first) first = row_pos[h] - window + 1;
     row_lo[h] = first;
     row_pen[h] = (rr % group) * 128 + rr / group + 63;
-    const bool with_sink = sink != nullptr && split == 0;
+    const bool with_sink = sink != nullptr && split == 0 && (!share_keys || warp == 0);
     m_run[h] = with_sink ? sink[row_head[h]] * 1.4426950408889634f : -INFINITY;
     l_run[h] = with_sink && (lane & 3) == 0 ? 1.f : 0.f;      // the row's sum is spread over its four lanes
   }
@@ -190,7 +198,65 @@ sink_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     const uint8_t* kt = k_tiles + buf * K_BYTES;
     const uint8_t* vt = v_tiles + buf * V_BYTES;
     const int j0 = (page_lo + t_begin + t) * SB_PAGE_TOKENS;
-    if (warp_live) {
+    if (share_keys) {
+      // this warp's 16 keys of the page: S (two blocks of 8 keys), softmax, one k-step of P V
+      float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        uint32_t b0, b1, b2, b3;
+        const int key = warp * 16 + (lane & 7) + (lane >> 4) * 8;
+        sk_ldm4(sk_smem(kt + sk_offset<D>(key, 2 * kk + ((lane >> 3) & 1))), b0, b1, b2, b3);
+        sk_mma(s2[0], qf[kk], b0, b1);
+        sk_mma(s2[1], qf[kk], b2, b3);
+      }
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h = e >> 1;
+          const int jj = warp * 16 + nb * 8 + (lane & 3) * 2 + (e & 1);
+          float v = s2[nb][e] * scale_log2;
+          if (r1) v -= pen_tab[row_pen[h] - jj];
+          if (j0 + jj > row_pos[h] || j0 + jj < row_lo[h]) v = -INFINITY;
+          s2[nb][e] = v;
+          mx[h] = fmaxf(mx[h], v);
+        }
+      }
+      float alpha[2], m_use[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(m_run[h], mx[h]);
+        m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+        alpha[h] = exp2f(m_run[h] - m_use[h]);
+        m_run[h] = m_new;
+      }
+      uint32_t pf1[4];
+      float rs[2] = {0.f, 0.f};
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+        const float p0 = exp2f(s2[nb][0] - m_use[0]), p1 = exp2f(s2[nb][1] - m_use[0]);
+        const float p2 = exp2f(s2[nb][2] - m_use[1]), p3 = exp2f(s2[nb][3] - m_use[1]);
+        rs[0] += p0 + p1;
+        rs[1] += p2 + p3;
+        pf1[nb * 2] = sk_pack(p0, p1);
+        pf1[nb * 2 + 1] = sk_pack(p2, p3);
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * alpha[h] + rs[h];
+#pragma unroll
+      for (int n = 0; n < NBLK; n += 2) {
+        o[n][0] *= alpha[0]; o[n][1] *= alpha[0]; o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+        o[n + 1][0] *= alpha[0]; o[n + 1][1] *= alpha[0]; o[n + 1][2] *= alpha[1]; o[n + 1][3] *= alpha[1];
+        uint32_t b0, b1, b2, b3;
+        const int key = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        sk_ldm4_trans(sk_smem(vt + sk_offset<DV>(key, n + (lane >> 4))), b0, b1, b2, b3);
+        sk_mma(o[n], pf1, b0, b1);
+        sk_mma(o[n + 1], pf1, b2, b3);
+      }
+    } else if (warp_live) {
     // S = Q K^T for 64 keys: 8 blocks of 8 keys
     float s[8][4];
 #pragma unroll
@@ -283,6 +349,50 @@ sink_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
   }
+  if (share_keys) {
+    // the four warps' shares of the same 16 rows meet in shared memory (the tiles are done with)
+    constexpr int LD = DV + 2;                       // a row's accumulator, then its maximum and sum
+    float* meet = reinterpret_cast<float*>(sk_mem);  // [4 warps][16 rows][LD]
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float* mine = meet + (size_t)(warp * 16 + (lane >> 2) + 8 * h) * LD;
+#pragma unroll
+      for (int n = 0; n < NBLK; ++n)
+        *reinterpret_cast<float2*>(mine + n * 8 + (lane & 3) * 2) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
+      if ((lane & 3) == 0) {
+        mine[DV] = m_run[h];
+        mine[DV + 1] = l_run[h];
+      }
+    }
+    __syncthreads();
+    const size_t n_rows = (size_t)n_tokens * heads;
+    for (int idx = tid; idx < rows_valid * DV; idx += SK_THREADS) {
+      const int r = idx / DV, c = idx - r * DV;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < SK_WARPS; ++w) M = fmaxf(M, meet[(size_t)(w * 16 + r) * LD + DV]);
+      float L = 0.f, a = 0.f;
+#pragma unroll
+      for (int w = 0; w < SK_WARPS; ++w) {
+        const float* theirs = meet + (size_t)(w * 16 + r) * LD;
+        const float f = theirs[DV] == -INFINITY ? 0.f : exp2f(theirs[DV] - M);
+        L += f * theirs[DV + 1];
+        a += f * theirs[c];
+      }
+      const size_t grow = (tok0 + r / group) * heads + kvh * group + r % group;
+      if (n_splits == 1) {
+        out[grow * DV + c] = from_f<bf16>(a * (gate ? gate[grow] : 1.f) / L);
+      } else {
+        part_acc[((size_t)split * n_rows + grow) * DV + c] = a;
+        if (c == 0) {
+          part_ml[((size_t)split * n_rows + grow) * 2] = M;
+          part_ml[((size_t)split * n_rows + grow) * 2 + 1] = L;
+        }
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     if (!row_ok[h]) continue;
@@ -353,7 +463,7 @@ static int sk_launch(const void* q, int q_stride, void* out, float* part_acc, fl
   const int tokens_per_block = SK_ROWS / group;
   int subs = (SB_PAGE_TOKENS + tokens_per_block - 1) / tokens_per_block;
   if (max_q_len > 0) subs = min(subs, (min(max_q_len, SB_PAGE_TOKENS) + tokens_per_block - 1) / tokens_per_block);
-  const int smem = SK_ROWS * D * 2 + 2 * SB_PAGE_TOKENS * (D + DV) * 2 + group * 128 * (int)sizeof(float);
+  const int smem = SK_ROWS * D * 2 + 2 * SB_PAGE_TOKENS * (D + DV) * 2 + group * 130 * (int)sizeof(float);
   static int configured = 0;
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(sink_attention_tc_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
