@@ -321,6 +321,166 @@ moe_tile_tc_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
   }
 }
 
+// The same for steps with many rows an expert (prompts): tiles of 128 rows times 128 outputs, eight warps
+// (two groups of 64 rows times four groups of 32 outputs), mma.sync m16n8k16 with operands by ldmatrix.
+// A warp's k-step of 16 is four A loads, two B loads and sixteen products (the 64 x 64 wmma tile above has
+// three loads for two products and is bound by them).  Rows and weights arrive in k-slices through a ring of
+// three cp.async stages; rows are padded by 16 bytes, so the eight 16-byte rows of an ldmatrix fall into
+// eight different bank groups.  The epilogue goes from the accumulators to global memory in pairs.
+#define MOE_BIG 128
+__device__ __forceinline__ void moe_ldm4(const void* p, uint32_t* r) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void moe_mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(256)
+moe_tile_big_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
+                    const int* __restrict__ sorted, const int* __restrict__ tile_expert,
+                    const int* __restrict__ n_tiles, int k_dim, int n_out, int top, float limit) {
+  constexpr bool UP = MODE != 0;
+  // k-slices of 64 (rows of 144 bytes) with one weight block, of 32 (rows of 80 bytes) with two: three stages
+  // of either leave room for two blocks an SM
+  constexpr int NW = MODE == 1 ? 2 : 1, BK = NW == 1 ? 64 : 32, LD = BK + 8, STAGES = 3;
+  constexpr int PIECES = BK / 8, PASS_ROWS = 256 / PIECES, PASSES = MOE_BIG / PASS_ROWS;
+  extern __shared__ __align__(128) unsigned char moe_smem[];
+  bf16* xs = reinterpret_cast<bf16*>(moe_smem);                          // [STAGES][128][LD]
+  bf16* ws = xs + STAGES * MOE_BIG * LD;                                 // [STAGES][NW][128][LD]
+  __shared__ int src[MOE_BIG];
+  // (launch_dependents comes at this kernel's end, as in the smaller tile: several waves of large blocks)
+  pdl_wait();
+  SB_BEHIND_WAIT(x);
+  SB_BEHIND_WAIT(sorted);
+  SB_BEHIND_WAIT(tile_expert);
+  SB_BEHIND_WAIT(n_tiles);
+  const int tile = blockIdx.x;
+  if (tile >= n_tiles[0]) return;
+  const int e = tile_expert[tile];
+  const int n0 = blockIdx.y * MOE_BIG;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < MOE_BIG) src[tid] = sorted[tile * MOE_BIG + tid];
+  __syncthreads();
+  const bf16* we = w + (size_t)e * NW * n_out * k_dim;
+  // this thread copies one 16-byte piece of PASSES rows (lm, lm + PASS_ROWS, ..) of every slice of rows and of weights
+  const int lm = tid / PIECES, lc = (tid % PIECES) * 8;
+  const bf16* x_row[PASSES];
+  const bf16* w_row[PASSES];
+  bool x_in[PASSES], w_in[PASSES];
+#pragma unroll
+  for (int h = 0; h < PASSES; ++h) {
+    const int r = lm + PASS_ROWS * h;
+    const int pair = src[r];
+    x_in[h] = pair >= 0;
+    x_row[h] = x + (UP ? (size_t)(pair >= 0 ? pair / top : 0) : (size_t)tile * MOE_BIG + r) * k_dim;
+    w_in[h] = n0 + r < n_out;
+    w_row[h] = we + (size_t)(w_in[h] ? n0 + r : 0) * k_dim;
+  }
+  const int k_tiles = (k_dim + BK - 1) / BK;
+  auto load = [&](int kt, int st) {
+    const int kk = kt * BK + lc;
+    const bool in_k = kk < k_dim;
+    const int ko = in_k ? kk : 0;
+#pragma unroll
+    for (int h = 0; h < PASSES; ++h) {
+      const int r = lm + PASS_ROWS * h;
+      moe_cp16(xs + ((size_t)st * MOE_BIG + r) * LD + lc, x_row[h] + ko, in_k && x_in[h]);
+#pragma unroll
+      for (int a = 0; a < NW; ++a)
+        moe_cp16(ws + (((size_t)st * NW + a) * MOE_BIG + r) * LD + lc, w_row[h] + (size_t)a * n_out * k_dim + ko,
+                 in_k && w_in[h]);
+    }
+  };
+  const int wm = warp & 1, wn = warp >> 1;               // rows 64 wm .., outputs 32 wn ..
+  float acc[NW][4][4][4];
+#pragma unroll
+  for (int a = 0; a < NW; ++a)
+#pragma unroll
+    for (int mb = 0; mb < 4; ++mb)
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[a][mb][nb][c] = 0.f;
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (st < k_tiles) load(st, st);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  const int a_row = wm * 64 + (lane & 15), a_col = (lane >> 4) * 8;
+  const int b_row = wn * 32 + (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
+  for (int kt = 0; kt < k_tiles; ++kt) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+    __syncthreads();
+    const int nk = kt + STAGES - 1;
+    if (nk < k_tiles) load(nk, nk % STAGES);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const int st = kt % STAGES;
+    const bf16* xt = xs + (size_t)st * MOE_BIG * LD;
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 16) {
+      uint32_t af[4][4];
+#pragma unroll
+      for (int mb = 0; mb < 4; ++mb) moe_ldm4(xt + (size_t)(a_row + mb * 16) * LD + kk + a_col, af[mb]);
+#pragma unroll
+      for (int a = 0; a < NW; ++a) {
+        const bf16* wt = ws + ((size_t)st * NW + a) * MOE_BIG * LD;
+#pragma unroll
+        for (int nb2 = 0; nb2 < 2; ++nb2) {
+          uint32_t bfr[4];
+          moe_ldm4(wt + (size_t)(b_row + nb2 * 16) * LD + kk + b_col, bfr);
+#pragma unroll
+          for (int mb = 0; mb < 4; ++mb) {
+            moe_mma(acc[a][mb][nb2 * 2], af[mb], bfr[0], bfr[1]);
+            moe_mma(acc[a][mb][nb2 * 2 + 1], af[mb], bfr[2], bfr[3]);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  pdl_trigger();
+  // accumulator (mb, nb, c): row 64 wm + 16 mb + lane / 4 + 8 (c / 2), output 32 wn + 8 nb + 2 (lane % 4) + c % 2;
+  // n_out is even here (a multiple of 16), so a pair of outputs is inside or outside together
+#pragma unroll
+  for (int mb = 0; mb < 4; ++mb)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int m = wm * 64 + mb * 16 + (lane >> 2) + 8 * h;
+      const int row_pair = src[m];
+      if (MODE == 0 && row_pair < 0) continue;
+      bf16* y_row = y + (MODE == 0 ? (size_t)row_pair : (size_t)tile * MOE_BIG + m) * n_out;
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb) {
+        const int n = n0 + wn * 32 + nb * 8 + (lane & 3) * 2;
+        if (n >= n_out) continue;
+        float r0, r1;
+        if (MODE == 1) {
+          float g0 = rnd<bf16>(acc[0][mb][nb][2 * h]), g1 = rnd<bf16>(acc[0][mb][nb][2 * h + 1]);
+          float u0 = rnd<bf16>(acc[NW - 1][mb][nb][2 * h]), u1 = rnd<bf16>(acc[NW - 1][mb][nb][2 * h + 1]);
+          g0 = fminf(g0, limit);
+          g1 = fminf(g1, limit);
+          u0 = fminf(fmaxf(u0, -limit), limit);
+          u1 = fminf(fmaxf(u1, -limit), limit);
+          r0 = row_pair >= 0 ? g0 / (1.f + expf(-1.702f * g0)) * (u0 + 1.f) : 0.f;
+          r1 = row_pair >= 0 ? g1 / (1.f + expf(-1.702f * g1)) * (u1 + 1.f) : 0.f;
+        } else if (MODE == 2) {
+          const float u0 = fmaxf(rnd<bf16>(acc[0][mb][nb][2 * h]), 0.f), u1 = fmaxf(rnd<bf16>(acc[0][mb][nb][2 * h + 1]), 0.f);
+          r0 = row_pair >= 0 ? u0 * u0 : 0.f;
+          r1 = row_pair >= 0 ? u1 * u1 : 0.f;
+        } else {
+          r0 = acc[0][mb][nb][2 * h];
+          r1 = acc[0][mb][nb][2 * h + 1];
+        }
+        *reinterpret_cast<__nv_bfloat162*>(y_row + n) = __floats2bfloat162_rn(r0, r1);
+      }
+    }
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ down, const float* __restrict__ weights, T* __restrict__ out,
                                    int width, int top) {
@@ -344,6 +504,14 @@ template <int MODE>
 static int moe_tiles_mode(int dtype, int tile_rows, const void* x, const void* w, void* y, const int* sorted,
                           const int* tile_expert, const int* n_tiles, int max_tiles, int k_dim, int n_out, int top,
                           float limit, cudaStream_t s) {
+  if (tile_rows == MOE_BIG) {
+    if (dtype != 1 || k_dim % 16 || n_out % 2 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)y % 4)) return -2;
+    constexpr int NW = MODE == 1 ? 2 : 1, LD = (NW == 1 ? 64 : 32) + 8;
+    const size_t smem = (size_t)3 * (1 + NW) * MOE_BIG * LD * sizeof(bf16);
+    cudaFuncSetAttribute(moe_tile_big_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_dependent(moe_tile_big_kernel<MODE>, dim3(max_tiles, (n_out + MOE_BIG - 1) / MOE_BIG), dim3(256), smem, s,
+                            (const bf16*)x, (const bf16*)w, (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
+  }
   const dim3 grid(max_tiles, (n_out + MOE_BN - 1) / MOE_BN);
   if (tile_rows == MOE_TC_BM) {
     if (dtype != 1 || k_dim % 16 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16)) return -2;
@@ -367,6 +535,13 @@ extern "C" {
 // inner size multiples of 16), else 32.
 int sb_moe_tile_rows(int dtype, int width, int inner) {
   return dtype == 1 && width % 16 == 0 && inner % 16 == 0 ? MOE_TC_BM : MOE_BM;
+}
+// The same for a step of `n_pairs` (row, expert) pairs over `experts` experts: 128 when the tensor-core tiles
+// take the operands and an expert has 128 rows or more on average (the large tiles pay for their padding
+// from there on), else as above.
+int sb_moe_tile_rows_for(int dtype, int width, int inner, long long n_pairs, int experts) {
+  const int rows = sb_moe_tile_rows(dtype, width, inner);
+  return rows == MOE_TC_BM && n_pairs >= (long long)MOE_BIG * experts ? MOE_BIG : rows;
 }
 int sb_moe_max_experts() { return MOE_MAX_EXPERTS; }
 int sb_moe_max_top() { return MOE_MAX_TOP; }

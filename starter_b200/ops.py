@@ -1633,12 +1633,14 @@ def moe_route(h, router, router_bias, top, scoring="softmax_top", weight_scale=1
     return ids, weights
 
 
-def moe_experts(h, ids, weights, gate_up, down, limit=0.0, expert="gated_clamped"):
+def moe_experts(h, ids, weights, gate_up, down, limit=0.0, expert="gated_clamped", tile_rows=None):
     """The chosen experts of every row and their weighted sum: ``gate_up`` ``[E, 2 * F, W]`` (an expert's
     gate rows, then its up rows), ``down`` ``[E, W, F]``; an expert is ``down(g * sigmoid(1.702 g) * (u +
     1))`` with ``g = min(gate(h), limit)`` and ``u = clamp(up(h), -limit, limit)``.  With ``expert``
     ``"relu2"`` the experts have no gate: ``gate_up`` is ``[E, F, W]`` and an expert is
-    ``down(relu(up(h))^2)``.  Returns ``[T, W]``."""
+    ``down(relu(up(h))^2)``.  Returns ``[T, W]``.  ``tile_rows`` names the tile kind (32: plain; 64 and 128:
+    tensor cores) instead of the one the step's shape chooses: steps with 128 rows an expert or more take the
+    large tiles."""
     if expert not in MOE_EXPERTS:
         raise KernelError(f"no expert kind {expert!r} (known: {', '.join(MOE_EXPERTS)})")
     up_mode = MOE_EXPERTS[expert]
@@ -1654,8 +1656,13 @@ def moe_experts(h, ids, weights, gate_up, down, limit=0.0, expert="gated_clamped
     if tuple(gate_up.shape) != (experts, (2 if up_mode == 1 else 1) * inner, width) or tuple(down.shape) != (experts, width, inner):
         raise KernelError(f"expert weights {tuple(gate_up.shape)} / {tuple(down.shape)} do not fit rows of {width}")
     lib = _lib("moe")
-    bm = lib.sb_moe_tile_rows(_code(h.dtype), width, inner)     # 64: tensor-core tiles; 32: the plain ones
     n_pairs = n_tokens * top
+    # 64 and 128: tensor-core tiles (128 with many rows an expert); 32: the plain ones
+    bm = lib.sb_moe_tile_rows_for(_code(h.dtype), width, inner, ctypes.c_longlong(n_pairs), experts)
+    if tile_rows is not None:
+        if tile_rows not in (32, 64, 128) or (tile_rows > 32 and lib.sb_moe_tile_rows(_code(h.dtype), width, inner) != 64):
+            raise KernelError(f"no expert tiles of {tile_rows} rows for {h.dtype}, width {width}, inner size {inner}")
+        bm = int(tile_rows)
     max_tiles = -(-n_pairs // bm) + min(experts, n_pairs)
     capacity = max_tiles * bm
     meta = torch.empty((capacity + max_tiles + 1,), dtype=torch.int32, device=h.device)

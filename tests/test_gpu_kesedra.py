@@ -453,6 +453,33 @@ def test_experts_alone(experts, top, width, inner, rows, dtype):
     close(out, want, dtype, f"{rows} rows, {experts} experts")
 
 
+@pytest.mark.parametrize("experts, top, width, inner", [(3, 2, 144, 80), (4, 1, 256, 128)])
+def test_experts_on_every_tile_kind(experts, top, width, inner):
+    """600 rows, so that the step chooses the tiles of 128 rows: those, the tiles of 64 and the plain tiles
+    against the plain experts, with sizes that end inside a k-slice and inside a tile's outputs."""
+    from starter_b200 import ops
+
+    rows = 600
+    g = torch.Generator().manual_seed(experts + width)
+    h = dev(torch.randn(rows, width, generator=g), torch.bfloat16)
+    gate_up = dev(torch.randn(experts, 2 * inner, width, generator=g) * 0.3, torch.bfloat16)
+    down = dev(torch.randn(experts, width, inner, generator=g) * 0.2, torch.bfloat16)
+    ids = torch.stack([torch.randperm(experts, generator=g)[:top] for _ in range(rows)]).to(torch.int32)
+    weights = torch.softmax(torch.randn(rows, top, generator=g), dim=-1)
+    h64 = h.double().cpu()
+    want = torch.zeros(rows, width, dtype=F)
+    for e in range(experts):
+        w = {"e.gate": gate_up[e, :inner].double().cpu(), "e.up": gate_up[e, inner:].double().cpu(),
+             "e.down": down[e].double().cpu()}
+        share = (weights * (ids == e)).sum(dim=1).double()
+        used = share > 0
+        want[used] += share[used, None] * plain.expert(h64[used], w, "e.", 1.25)
+    assert ops._lib("moe").sb_moe_tile_rows_for(1, width, inner, rows * top, experts) == 128
+    for tile_rows in (None, 32, 64, 128):
+        out = ops.moe_experts(h, ids.cuda(), weights.cuda(), gate_up, down, 1.25, tile_rows=tile_rows)
+        close(out, want, "bfloat16", f"tiles of {tile_rows or 'the chosen'} rows")
+
+
 # ------------------------------------------------------------------------------ the model
 
 def all_places(n):

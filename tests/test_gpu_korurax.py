@@ -397,6 +397,39 @@ def test_squared_relu_experts_alone(experts, top, width, inner, rows, dtype):
     close(got, want, dtype, "experts", bf16=2.5e-2)
 
 
+@pytest.mark.parametrize("rows", [3, 700])
+@pytest.mark.parametrize("experts, top, width, inner", [(3, 2, 144, 80), (4, 1, 256, 128), (5, 3, 48, 272)])
+def test_squared_relu_experts_on_every_tile_kind(experts, top, width, inner, rows):
+    """The plain tiles and both tensor-core tiles (64 rows; 128 rows, which steps with many rows an expert
+    choose) against the experts one by one: inner sizes and widths that end inside a k-slice and inside a
+    tile's outputs, one expert with a handful of rows next to experts with hundreds."""
+    from starter_b200 import ops
+
+    g = torch.Generator().manual_seed(rows * experts + width)
+    h = dev(torch.randn(rows, width, generator=g, dtype=F), torch.bfloat16)
+    up = dev(torch.randn(experts, inner, width, generator=g, dtype=F) * 0.2, torch.bfloat16)
+    down = dev(torch.randn(experts, width, inner, generator=g, dtype=F) * 0.2, torch.bfloat16)
+    ids = torch.stack([torch.randperm(experts - 1, generator=g)[:top] for _ in range(rows)]).to(torch.int32)
+    ids[:min(rows, 5), 0] = experts - 1          # the last expert serves five rows at most
+    if top > 1:
+        ids[:min(rows, 5), 1:] = torch.arange(top - 1, dtype=torch.int32)
+    weights = torch.rand(rows, top, generator=g, dtype=F) + 0.1
+    hd, ud, dd = h.double().cpu(), up.double().cpu(), down.double().cpu()
+    want = torch.zeros(rows, width, dtype=F)
+    for e in range(experts):
+        chosen = (ids == e)
+        share = (weights * chosen).sum(dim=1)
+        used = share > 0
+        want[used] += share[used, None] * ((torch.relu(hd[used] @ ud[e].T) ** 2) @ dd[e].T)
+    if rows * top >= 128 * experts:
+        assert ops._lib("moe").sb_moe_tile_rows_for(1, width, inner, rows * top, experts) == 128
+    got = ops.moe_experts(h, dev(ids, torch.int32), dev(weights), up, down, expert="relu2")
+    close(got, want, "bfloat16", "the tiles the step chooses", bf16=2.5e-2)
+    for tile_rows in (32, 64, 128):
+        got = ops.moe_experts(h, dev(ids, torch.int32), dev(weights), up, down, expert="relu2", tile_rows=tile_rows)
+        close(got, want, "bfloat16", f"tiles of {tile_rows} rows", bf16=2.5e-2)
+
+
 # ------------------------------------------------------------------------------ the model
 
 def all_places(n):
