@@ -116,6 +116,13 @@ struct PromptGemmArgs {
   unsigned long long wait_limit_ns;
   int withhold_kblock;  // >= 0: the first CTA leaves out its weight copy of this k-block of its first tile
   float limit;          // the clamp of the gated activation with code 3
+  // grouped (tile_expert given): every row tile of 256 rows belongs to one of several weight matrices of
+  // equal shape that follow each other in w; how many row tiles there are stands on the device
+  const int* tile_expert;   // [>= the row tiles]: which weight matrix a row tile takes, or null
+  const int* m_tiles_dev;   // the number of row tiles (at most m_tiles)
+  const int* row_map;       // [rows] or null: the row of `out` a row's result goes to (negative: nowhere)
+  int expert_rows;          // weight rows per matrix (n_out; 2 * n_out with gated)
+  int act;                  // without gate: 0 the product itself, 1 relu(round(product))^2
 };
 
 // ------------------------------------------------------------------------------------------ kernel
@@ -125,10 +132,10 @@ struct PromptGemmArgs {
 // one weight tile follow each other, then the next weight tile.  So at any time the pairs work on
 // about group_m row tiles x a few weight tiles, the group's rows of x stay in L2 while all weight
 // tiles pass, and the weights are read from memory once per group.
-__device__ __forceinline__ void pg_tile(const PromptGemmArgs& args, int t, int& mt, int& nt) {
+__device__ __forceinline__ void pg_tile(const PromptGemmArgs& args, int m_tiles, int t, int& mt, int& nt) {
   const int per_group = args.group_m * args.n_tiles;
   const int g = t / per_group, r = t - g * per_group;
-  const int here = min(args.group_m, args.m_tiles - g * args.group_m);
+  const int here = min(args.group_m, m_tiles - g * args.group_m);
   nt = r / here;
   mt = g * args.group_m + (r - nt * here);
 }
@@ -138,6 +145,10 @@ __device__ __forceinline__ void pg_tile(const PromptGemmArgs& args, int t, int& 
 // more: what a separate add of two bfloat16 tensors gives, engine/engine.py:734-736).
 __device__ __forceinline__ void pg_store32(const PromptGemmArgs& args, int grow, int col, float* v) {
   if (grow >= args.rows || col >= args.n_out) return;
+  if (args.row_map) {
+    grow = args.row_map[grow];
+    if (grow < 0) return;
+  }
   const size_t offset = (size_t)grow * args.n_out + col;
   bf16* at = args.out + offset;
   const bool wide = args.n_out % 8 == 0 && col + 32 <= args.n_out;
@@ -192,7 +203,9 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
   const uint32_t rank = pg_cluster_rank();                     // 0: the CTA that issues the MMAs
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const int n_tiles_total = args.m_tiles * args.n_tiles;
+  const bool grouped = args.tile_expert != nullptr;
+  // (grouped: every role reads the number of row tiles from the device behind its own pdl_wait)
+  int n_tiles_total = args.m_tiles * args.n_tiles;
   const int n_kb = (args.k_dim + PG_TILE_K - 1) / PG_TILE_K;
   const int out_per_tile = GATED ? half_n : args.bn;           // output columns a tile covers
 
@@ -215,14 +228,17 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     // ---------------- producer: the warp walks the ring together, one elected lane issues the copies
     const bool elected = elect_one();
     pdl_wait();
+    const int m_tiles = grouped ? min(*args.m_tiles_dev, args.m_tiles) : args.m_tiles;
+    n_tiles_total = m_tiles * args.n_tiles;
     int it = 0, s = 0;
     uint32_t parity = 1;          // flips at every wrap of the ring; the first pass waits for nothing
     bool gave_up = false;
     for (int t = pair; t < n_tiles_total && !gave_up; t += n_pairs) {
       int mt, nt;
-      pg_tile(args, t, mt, nt);
+      pg_tile(args, m_tiles, t, mt, nt);
       const int m0 = mt * PG_TILE_M + (int)rank * PG_ROWS_PER_CTA;
-      const int w0 = GATED ? (rank == 0 ? nt * half_n : args.n_out + nt * half_n) : nt * args.bn + (int)rank * half_n;
+      const int w0 = (grouped ? args.tile_expert[mt] * args.expert_rows : 0) +
+                     (GATED ? (rank == 0 ? nt * half_n : args.n_out + nt * half_n) : nt * args.bn + (int)rank * half_n);
       const bool withheld_tile = rank == 0 && t == pair;
       for (int kb = 0; kb < n_kb; ++kb, ++it) {
         if (it >= STAGES && !__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], parity, abort, limit))) { gave_up = true; break; }
@@ -249,6 +265,10 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     if (rank == 0) {
       const bool elected = elect_one();
       const uint32_t idesc = pg_instr_desc(args.bn);
+      if (grouped) {
+        pdl_wait();
+        n_tiles_total = min(*args.m_tiles_dev, args.m_tiles) * args.n_tiles;
+      }
       int it = 0, i = 0, s = 0;
       uint32_t parity = 0;
       bool gave_up = false;
@@ -289,6 +309,8 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
     const uint32_t empty0 = pg_in_cta(smem_u32(&acc_empty[0]), 0), empty1 = pg_in_cta(smem_u32(&acc_empty[1]), 0);
     pdl_wait();   // before the first store: the output may be memory an earlier kernel still reads
+    const int m_tiles = grouped ? min(*args.m_tiles_dev, args.m_tiles) : args.m_tiles;
+    n_tiles_total = m_tiles * args.n_tiles;
     int i = 0;
     for (int t = pair; t < n_tiles_total; t += n_pairs, ++i) {
       const int b = i & 1;
@@ -296,7 +318,7 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
       if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[b], (i >> 1) & 1, abort, limit))) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       int mt, nt;
-      pg_tile(args, t, mt, nt);
+      pg_tile(args, m_tiles, t, mt, nt);
       const int grow = mt * PG_TILE_M + (int)rank * PG_ROWS_PER_CTA + row;
       const int col0 = nt * out_per_tile;
       const uint32_t acc = lane_base + (uint32_t)b * PG_ACC_STRIDE;
@@ -313,6 +335,13 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             const float gr = rnd<bf16>(v[j]), ur = rnd<bf16>(u[j]);
             if (args.gated == SB_ACT_CLAMPED) v[j] = gate_clamped(gr, ur, args.limit);
             else v[j] = rnd<bf16>(args.gated == SB_ACT_GELU_TANH ? gate_act_fast(gr, SB_ACT_GELU_TANH) : gr / (1.f + __expf(-gr))) * ur;
+          }
+        }
+        if (!GATED && args.act == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float u = fmaxf(rnd<bf16>(v[j]), 0.f);
+            v[j] = u * u;
           }
         }
         if (c == n_chunks - 1) {
@@ -413,12 +442,79 @@ static int pg_entry(const void* x, const void* w, void* out, const void* residua
   args.group_m = (int)group_m;
   args.wait_limit_ns = wait_limit_ns; args.withhold_kblock = withhold_kblock;
   args.limit = limit;
+  args.tile_expert = nullptr; args.m_tiles_dev = nullptr; args.row_map = nullptr; args.expert_rows = 0; args.act = 0;
+  const int smem = stages * stage_bytes + 1024;
+  return gated ? pg_launch<true>(map_x, map_w, args, pairs, smem, s)
+               : pg_launch<false>(map_x, map_w, args, pairs, smem, s);
+}
+
+// The grouped product: x [rows, k_dim] whose rows stand in tiles of 256 that each belong to one of `experts`
+// weight matrices w [experts, n_out (2 * n_out if gated), k_dim]; tile_expert [max_m_tiles] names the matrix of
+// every row tile and m_tiles_dev [1] says how many row tiles there are (both on the device, written by an
+// earlier kernel of the stream: the host never learns them).  rows >= 256 * max_m_tiles.  out [rows, n_out], or
+// with row_map [rows] the row row_map[r] of out for row r (none if negative).  act 1: relu(product)^2.
+static int pg_entry_grouped(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, int experts,
+                            const int* tile_expert, const int* m_tiles_dev, int max_m_tiles, const int* row_map,
+                            int gated, int act, float limit, int* status, cudaStream_t s) {
+  if (max_m_tiles == 0 || n_out == 0) return 0;
+  if (k_dim % 8 || k_dim <= 0 || experts < 1 || !tile_expert || !m_tiles_dev) return -2;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return -2;
+  if ((long long)max_m_tiles * PG_TILE_M > rows) return -2;
+  if (gated && act) return -2;
+  const long long expert_rows = gated ? 2ll * n_out : n_out;
+  if (expert_rows * experts > 0x7fffffffll) return -2;
+  int pairs = pg_sm_count() / 2;
+  if (pairs < 1) return -2;
+  // the weight rows per tile by the same estimate as the plain product, for the most row tiles there can be
+  int bn = 0;
+  long long best = -1;
+  const int candidates[4] = {256, 192, 160, 128};
+  for (int c = 0; c < 4; ++c) {
+    const int cand = candidates[c];
+    if (gated && cand % 64) continue;
+    const int per = gated ? cand / 2 : cand;
+    const long long tiles = (long long)max_m_tiles * ((n_out + per - 1) / per);
+    const long long cost = ((tiles + pairs - 1) / pairs) * (cand + 144);
+    if (best < 0 || cost < best) { best = cost; bn = cand; }
+  }
+  const int per = gated ? bn / 2 : bn;
+  const int n_tiles = (n_out + per - 1) / per;
+  const int stage_bytes = PG_A_BYTES + (bn / 2) * PG_TILE_K * 2;
+  int stages = (227 * 1024 - 1024 - 1024) / stage_bytes;
+  if (stages > PG_MAX_STAGES) stages = PG_MAX_STAGES;
+  if (stages < 2) return -2;
+  const long long total = (long long)max_m_tiles * n_tiles;
+  if (total < pairs) pairs = (int)total;
+  CUtensorMap map_x, map_w;
+  int rc = sb_make_map(&map_x, x, rows, k_dim, PG_ROWS_PER_CTA);
+  if (rc) return rc;
+  rc = sb_make_map(&map_w, w, expert_rows * experts, k_dim, bn / 2);
+  if (rc) return rc;
+  PromptGemmArgs args;
+  args.out = (bf16*)out; args.residual = nullptr; args.status = status;
+  args.rows = rows; args.n_out = n_out; args.k_dim = k_dim;
+  args.bn = bn; args.stages = stages; args.gated = gated;
+  args.m_tiles = max_m_tiles; args.n_tiles = n_tiles;
+  // an expert's row tiles follow each other: a group of a few row tiles shares its weight tiles in L2
+  args.group_m = max_m_tiles < 4 ? max_m_tiles : 4;
+  args.wait_limit_ns = TC_WAIT_LIMIT_NS; args.withhold_kblock = -1;
+  args.limit = limit;
+  args.tile_expert = tile_expert; args.m_tiles_dev = m_tiles_dev; args.row_map = row_map;
+  args.expert_rows = (int)expert_rows; args.act = act;
   const int smem = stages * stage_bytes + 1024;
   return gated ? pg_launch<true>(map_x, map_w, args, pairs, smem, s)
                : pg_launch<false>(map_x, map_w, args, pairs, smem, s);
 }
 
 extern "C" {
+
+// See pg_entry_grouped.  gated: 0, or the code of a gated activation (3: the clamped gate with `limit`).
+int sb_gemm_prompt_grouped(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, int experts,
+                           const int* tile_expert, const int* m_tiles_dev, int max_m_tiles, const int* row_map,
+                           int gated, int act, float limit, int* status, cudaStream_t s) {
+  return pg_entry_grouped(x, w, out, rows, n_out, k_dim, experts, tile_expert, m_tiles_dev, max_m_tiles, row_map,
+                          gated, act, limit, status, s);
+}
 
 int sb_gemm_prompt(const void* x, const void* w, void* out, const void* residual, int rows, int n_out, int k_dim, int bn, int pairs,
                    int gated, int* status, cudaStream_t s) {

@@ -481,6 +481,23 @@ moe_tile_big_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16
     }
 }
 
+// The rows of h in the order of `sorted` (a pair's row is h[pair / top]; zeros where a tile is padded), for a
+// product that wants its rows in place: a block a row, 16-byte pieces.  Rows behind the last tile stay unwritten.
+__global__ void moe_gather_kernel(const bf16* __restrict__ h, const int* __restrict__ sorted,
+                                  const int* __restrict__ n_tiles, int tile_rows, int top, bf16* __restrict__ out,
+                                  int width) {
+  pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
+  SB_BEHIND_WAIT(h);
+  SB_BEHIND_WAIT(sorted);
+  SB_BEHIND_WAIT(n_tiles);
+  const int row = blockIdx.x;
+  if (row >= n_tiles[0] * tile_rows) return;
+  const int pair = sorted[row];
+  const uint4* from = reinterpret_cast<const uint4*>(h + (size_t)(pair >= 0 ? pair / top : 0) * width);
+  uint4* to = reinterpret_cast<uint4*>(out + (size_t)row * width);
+  for (int c = threadIdx.x; c < width / 8; c += blockDim.x) to[c] = pair >= 0 ? from[c] : make_uint4(0u, 0u, 0u, 0u);
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ down, const float* __restrict__ weights, T* __restrict__ out,
                                    int width, int top) {
@@ -536,12 +553,25 @@ extern "C" {
 int sb_moe_tile_rows(int dtype, int width, int inner) {
   return dtype == 1 && width % 16 == 0 && inner % 16 == 0 ? MOE_TC_BM : MOE_BM;
 }
-// The same for a step of `n_pairs` (row, expert) pairs over `experts` experts: 128 when the tensor-core tiles
-// take the operands and an expert has 128 rows or more on average (the large tiles pay for their padding
-// from there on), else as above.
+// The same for a step of `n_pairs` (row, expert) pairs over `experts` experts: when the tensor-core tiles take
+// the operands, 128 from 128 rows an expert on average (the large tiles pay for their padding from there
+// on) and 256 from 256 (the row tiles of the grouped tcgen05 product, which runs in place of these tiles);
+// else as above.
 int sb_moe_tile_rows_for(int dtype, int width, int inner, long long n_pairs, int experts) {
   const int rows = sb_moe_tile_rows(dtype, width, inner);
-  return rows == MOE_TC_BM && n_pairs >= (long long)MOE_BIG * experts ? MOE_BIG : rows;
+  if (rows != MOE_TC_BM) return rows;
+  // 256: the grouped tcgen05 product (its row tiles), from 256 rows an expert on average
+  if (n_pairs >= 256ll * experts) return 256;
+  return n_pairs >= (long long)MOE_BIG * experts ? MOE_BIG : rows;
+}
+
+// h [.., width] bfloat16 with width a multiple of 8, 16-byte aligned; out [capacity, width].
+int sb_moe_gather(const void* h, const int* sorted, const int* n_tiles, int tile_rows, int top, void* out, int capacity,
+                  int width, cudaStream_t s) {
+  if (capacity == 0) return 0;
+  if (width % 8 || ((uintptr_t)h % 16) || ((uintptr_t)out % 16) || top < 1) return -2;
+  return launch_dependent(moe_gather_kernel, dim3(capacity), dim3(width / 8 >= 256 ? 256 : 128), 0, s, (const bf16*)h,
+                          sorted, n_tiles, tile_rows, top, (bf16*)out, width);
 }
 int sb_moe_max_experts() { return MOE_MAX_EXPERTS; }
 int sb_moe_max_top() { return MOE_MAX_TOP; }

@@ -179,6 +179,8 @@ def rmsnorm(x, gain, eps, delta=None, rows=None, out=None):
 
 #: the activations a gated product knows, and the code the kernels take for each
 ACTIVATIONS = {"silu": 1, "gelu_tanh": 2}
+#: the code of the clamped gate ``min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1)``, which takes its limit beside it
+GATE_CLAMPED = 3
 
 
 def gate_code(gated) -> int:
@@ -1633,14 +1635,15 @@ def moe_route(h, router, router_bias, top, scoring="softmax_top", weight_scale=1
     return ids, weights
 
 
-def moe_experts(h, ids, weights, gate_up, down, limit=0.0, expert="gated_clamped", tile_rows=None):
+def moe_experts(h, ids, weights, gate_up, down, limit=0.0, expert="gated_clamped", tile_rows=None, status=None):
     """The chosen experts of every row and their weighted sum: ``gate_up`` ``[E, 2 * F, W]`` (an expert's
     gate rows, then its up rows), ``down`` ``[E, W, F]``; an expert is ``down(g * sigmoid(1.702 g) * (u +
     1))`` with ``g = min(gate(h), limit)`` and ``u = clamp(up(h), -limit, limit)``.  With ``expert``
     ``"relu2"`` the experts have no gate: ``gate_up`` is ``[E, F, W]`` and an expert is
     ``down(relu(up(h))^2)``.  Returns ``[T, W]``.  ``tile_rows`` names the tile kind (32: plain; 64 and 128:
-    tensor cores) instead of the one the step's shape chooses: steps with 128 rows an expert or more take the
-    large tiles."""
+    ``mma.sync`` tiles; 256: the grouped tcgen05 product over rows gathered in the experts' order) instead of
+    the one the step's shape chooses: 128 from 128 rows an expert on average, 256 from 256.  ``status``: the
+    device word a tcgen05 wait that ran out is noted in."""
     if expert not in MOE_EXPERTS:
         raise KernelError(f"no expert kind {expert!r} (known: {', '.join(MOE_EXPERTS)})")
     up_mode = MOE_EXPERTS[expert]
@@ -1660,7 +1663,7 @@ def moe_experts(h, ids, weights, gate_up, down, limit=0.0, expert="gated_clamped
     # 64 and 128: tensor-core tiles (128 with many rows an expert); 32: the plain ones
     bm = lib.sb_moe_tile_rows_for(_code(h.dtype), width, inner, ctypes.c_longlong(n_pairs), experts)
     if tile_rows is not None:
-        if tile_rows not in (32, 64, 128) or (tile_rows > 32 and lib.sb_moe_tile_rows(_code(h.dtype), width, inner) != 64):
+        if tile_rows not in (32, 64, 128, 256) or (tile_rows > 32 and lib.sb_moe_tile_rows(_code(h.dtype), width, inner) != 64):
             raise KernelError(f"no expert tiles of {tile_rows} rows for {h.dtype}, width {width}, inner size {inner}")
         bm = int(tile_rows)
     max_tiles = -(-n_pairs // bm) + min(experts, n_pairs)
@@ -1671,10 +1674,26 @@ def moe_experts(h, ids, weights, gate_up, down, limit=0.0, expert="gated_clamped
                           bm, _stream())
     _check(rc, "moe_align")
     act = torch.empty((capacity, inner), dtype=h.dtype, device=h.device)
+    per_pair = torch.empty((n_pairs, width), dtype=h.dtype, device=h.device)
+    if bm == 256:
+        grouped = _lib("gemm_prompt_tcgen05").sb_gemm_prompt_grouped
+        gathered = torch.empty((capacity, width), dtype=h.dtype, device=h.device)
+        rc = lib.sb_moe_gather(_ptr(h), _ptr(sorted_pairs), _ptr(n_tiles), bm, top, _ptr(gathered), capacity, width, _stream())
+        _check(rc, "moe_gather")
+        rc = grouped(_ptr(gathered), _ptr(gate_up), _ptr(act), capacity, inner, width, experts, _ptr(tile_expert),
+                     _ptr(n_tiles), max_tiles, None, GATE_CLAMPED if up_mode == 1 else 0, 1 if up_mode == 2 else 0,
+                     ctypes.c_float(limit), _ptr(status), _stream())
+        _check(rc, "moe_up (grouped tcgen05)")
+        rc = grouped(_ptr(act), _ptr(down), _ptr(per_pair), capacity, width, inner, experts, _ptr(tile_expert),
+                     _ptr(n_tiles), max_tiles, _ptr(sorted_pairs), 0, 0, ctypes.c_float(0.0), _ptr(status), _stream())
+        _check(rc, "moe_down (grouped tcgen05)")
+        out = torch.empty_like(h)
+        rc = lib.sb_moe_combine(_code(h.dtype), _ptr(per_pair), _ptr(weights), _ptr(out), n_tokens, width, top, _stream())
+        _check(rc, "moe_combine")
+        return out
     rc = lib.sb_moe_tiles(_code(h.dtype), up_mode, bm, _ptr(h), _ptr(gate_up), _ptr(act), _ptr(sorted_pairs), _ptr(tile_expert),
                           _ptr(n_tiles), max_tiles, width, inner, top, ctypes.c_float(limit), _stream())
     _check(rc, "moe_up")
-    per_pair = torch.empty((n_pairs, width), dtype=h.dtype, device=h.device)
     rc = lib.sb_moe_tiles(_code(h.dtype), 0, bm, _ptr(act), _ptr(down), _ptr(per_pair), _ptr(sorted_pairs),
                           _ptr(tile_expert), _ptr(n_tiles), max_tiles, inner, width, top, ctypes.c_float(limit), _stream())
     _check(rc, "moe_down")

@@ -135,7 +135,8 @@ class RoutedExperts(Part):
         s = self.spec
         ids, weights = ops.moe_route(x, self.router, self.router_bias, s.top, s.scoring, s.weight_scale)
         self.last_ids = ids
-        return ops.moe_experts(x, ids, weights, self.gate_up, self.down, s.limit, s.expert)
+        return ops.moe_experts(x, ids, weights, self.gate_up, self.down, s.limit, s.expert,
+                               status=ctx.status if ctx is not None else None)
 
     def weight_bytes(self):
         """What a step reads at most: the router and every expert (a step of few tokens reads only the
