@@ -208,9 +208,10 @@ moe_tile_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict_
 
 // The same on the tensor cores (bfloat16, k a multiple of 16): tiles of 64 rows times 64 outputs, eight
 // warps (four groups of 16 rows times two halves of the outputs), wmma 16 x 16 x 16 with float
-// accumulators.  Rows (gathered through `sorted`) and weights arrive in k-slices of 32 through a ring of
+// accumulators.  Rows (gathered through `sorted`) and weights arrive in k-slices of 64 through a ring of
 // three cp.async stages, so that the copies of the next two slices are in flight while one is multiplied.
 #define MOE_TC_BM 64
+#define MOE_TC_BK 64
 __device__ __forceinline__ void moe_cp16(void* dst, const void* src, bool real) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
   const int bytes = real ? 16 : 0;
@@ -224,11 +225,15 @@ moe_tile_tc_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
                    const int* __restrict__ n_tiles, int k_dim, int n_out, int top, float limit) {
   using namespace nvcuda;
   constexpr bool UP = MODE != 0;
-  constexpr int BK = 32, LD = BK + 8, NW = MODE == 1 ? 2 : 1, STAGES = 3, CLD = MOE_BN + 4;
+  constexpr int BK = MOE_TC_BK, LD = BK + 8, NW = MODE == 1 ? 2 : 1, STAGES = 3, CLD = MOE_BN + 4;
+  constexpr int PIECES = BK / 8, PASS_ROWS = 256 / PIECES, PASSES = MOE_TC_BM / PASS_ROWS;
   extern __shared__ __align__(128) unsigned char moe_smem[];
   bf16* xs = reinterpret_cast<bf16*>(moe_smem);                          // [STAGES][64][LD]
   bf16* ws = xs + STAGES * MOE_TC_BM * LD;                               // [STAGES][NW][64][LD]
-  float* cs = reinterpret_cast<float*>(ws + STAGES * NW * MOE_BN * LD);  // [NW][64][CLD]
+  // [NW][64][CLD], in the ring's place once the last slice is multiplied (the ring is the larger of the two)
+  float* cs = reinterpret_cast<float*>(moe_smem);
+  static_assert((size_t)NW * MOE_TC_BM * CLD * sizeof(float) <= (size_t)STAGES * (1 + NW) * MOE_TC_BM * LD * sizeof(bf16),
+                "the staging tile must fit in the ring");
   __shared__ int src[MOE_TC_BM];
   // (launch_dependents comes at this kernel's end, not its start: it runs in several waves of large blocks,
   // and a successor that starts early would only sit on the SMs its later waves need)
@@ -245,20 +250,33 @@ moe_tile_tc_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
   if (tid < MOE_TC_BM) src[tid] = sorted[tile * MOE_TC_BM + tid];
   __syncthreads();
   const bf16* we = w + (size_t)e * NW * n_out * k_dim;
-  const int lm = tid >> 2, lc = (tid & 3) * 8;          // this thread's row and 16-byte piece of every slice
-  const int pair = src[lm];
-  const bf16* x_row = x + (UP ? (size_t)(pair >= 0 ? pair / top : 0) : (size_t)tile * MOE_TC_BM + lm) * k_dim;
-  const bool w_in = n0 + lm < n_out;
-  const bf16* w_row = we + (size_t)(w_in ? n0 + lm : 0) * k_dim;
+  // this thread's 16-byte piece of PASSES rows (lm, lm + PASS_ROWS, ..) of every slice
+  const int lm = tid / PIECES, lc = (tid % PIECES) * 8;
+  const bf16* x_row[PASSES];
+  const bf16* w_row[PASSES];
+  bool x_in[PASSES], w_in[PASSES];
+#pragma unroll
+  for (int p = 0; p < PASSES; ++p) {
+    const int r = lm + PASS_ROWS * p;
+    const int pair = src[r];
+    x_in[p] = pair >= 0;
+    x_row[p] = x + (UP ? (size_t)(pair >= 0 ? pair / top : 0) : (size_t)tile * MOE_TC_BM + r) * k_dim;
+    w_in[p] = n0 + r < n_out;
+    w_row[p] = we + (size_t)(w_in[p] ? n0 + r : 0) * k_dim;
+  }
   const int k_tiles = (k_dim + BK - 1) / BK;
   auto load = [&](int kt, int st) {
     const int kk = kt * BK + lc;
     const bool in_k = kk < k_dim;
-    moe_cp16(xs + ((size_t)st * MOE_TC_BM + lm) * LD + lc, x_row + (in_k ? kk : 0), in_k && pair >= 0);
 #pragma unroll
-    for (int a = 0; a < NW; ++a)
-      moe_cp16(ws + (((size_t)st * NW + a) * MOE_BN + lm) * LD + lc, w_row + (size_t)a * n_out * k_dim + (in_k ? kk : 0),
-               in_k && w_in);
+    for (int p = 0; p < PASSES; ++p) {
+      const int r = lm + PASS_ROWS * p;
+      moe_cp16(xs + ((size_t)st * MOE_TC_BM + r) * LD + lc, x_row[p] + (in_k ? kk : 0), in_k && x_in[p]);
+#pragma unroll
+      for (int a = 0; a < NW; ++a)
+        moe_cp16(ws + (((size_t)st * NW + a) * MOE_BN + r) * LD + lc, w_row[p] + (size_t)a * n_out * k_dim + (in_k ? kk : 0),
+                 in_k && w_in[p]);
+    }
   };
   const int wm = warp & 3, wn = warp >> 2;
   wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[NW][2];
@@ -294,6 +312,7 @@ moe_tile_tc_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   pdl_trigger();
+  __syncthreads();      // every warp is done with the ring before the staging tile takes its place
 #pragma unroll
   for (int a = 0; a < NW; ++a)
 #pragma unroll
@@ -481,6 +500,133 @@ moe_tile_big_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16
     }
 }
 
+// For steps with a handful of rows an expert (single tokens): a tile is up to MOE_FEW rows of one expert, kept
+// in shared memory as floats; a block takes MOE_FEW_NB weight rows, a warp one weight row at a time, which its
+// lanes read in 16-byte pieces (several in flight) and multiply with every row of the tile; sums in float,
+// joined by shuffles.  The weights are read once per tile and nothing is multiplied for padding: the step is
+// bound by the weights' bytes, not by tiles of 64 rows of which two are real.
+#define MOE_FEW 4
+#define MOE_FEW_NB 64
+#define MOE_FEW_MAX_K 12800
+__device__ __forceinline__ void moe_unpack8(const uint4& v, float* f) {
+  f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+  f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+  f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
+  f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(256)
+moe_few_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
+               const int* __restrict__ sorted, const int* __restrict__ tile_expert, const int* __restrict__ n_tiles,
+               int k_dim, int n_out, int top, float limit) {
+  constexpr bool UP = MODE != 0;
+  constexpr int NW = MODE == 1 ? 2 : 1;
+  extern __shared__ __align__(16) float moe_xf[];       // [MOE_FEW][k_dim]
+  __shared__ int src[MOE_FEW];
+  pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
+  SB_BEHIND_WAIT(x);
+  SB_BEHIND_WAIT(sorted);
+  SB_BEHIND_WAIT(tile_expert);
+  SB_BEHIND_WAIT(n_tiles);
+  const int tile = blockIdx.x;
+  if (tile >= n_tiles[0]) return;
+  const int e = tile_expert[tile];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < MOE_FEW) src[tid] = sorted[tile * MOE_FEW + tid];
+  __syncthreads();
+  int nr = 0;                                            // an expert's pairs fill its tiles from the front
+#pragma unroll
+  for (int r = 0; r < MOE_FEW; ++r)
+    if (src[r] >= 0) nr = r + 1;
+  const int chunks = k_dim / 8;
+  for (int r = 0; r < nr; ++r) {
+    const bf16* xr = x + (UP ? (size_t)(src[r] / top) : (size_t)tile * MOE_FEW + r) * k_dim;
+    for (int c = tid; c < chunks; c += 256) {
+      float f[8];
+      moe_unpack8(*reinterpret_cast<const uint4*>(xr + c * 8), f);
+      float4* to = reinterpret_cast<float4*>(moe_xf + (size_t)r * k_dim + c * 8);
+      to[0] = make_float4(f[0], f[1], f[2], f[3]);
+      to[1] = make_float4(f[4], f[5], f[6], f[7]);
+    }
+  }
+  __syncthreads();
+  const bf16* we = w + (size_t)e * NW * n_out * k_dim;
+  constexpr int PER_WARP = MOE_FEW_NB / 8;
+  const int n_first = blockIdx.y * MOE_FEW_NB + warp * PER_WARP;
+  if (n_first >= n_out) return;
+  // the warp walks k once: at every piece its PER_WARP weight rows' loads are in flight together, and the
+  // tile's rows of that piece are read from shared memory once for all of them
+  float acc[NW][PER_WARP][MOE_FEW];
+#pragma unroll
+  for (int a = 0; a < NW; ++a)
+#pragma unroll
+    for (int i = 0; i < PER_WARP; ++i)
+#pragma unroll
+      for (int r = 0; r < MOE_FEW; ++r) acc[a][i][r] = 0.f;
+  for (int c = lane; c < chunks; c += 32) {
+    float4 xv[MOE_FEW][2];
+#pragma unroll
+    for (int r = 0; r < MOE_FEW; ++r) {
+      if (r < nr) {
+        const float4* from = reinterpret_cast<const float4*>(moe_xf + (size_t)r * k_dim + c * 8);
+        xv[r][0] = from[0];
+        xv[r][1] = from[1];
+      } else {
+        xv[r][0] = xv[r][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+#pragma unroll
+    for (int a = 0; a < NW; ++a) {
+      uint4 wv[PER_WARP];
+#pragma unroll
+      for (int i = 0; i < PER_WARP; ++i) {
+        const int n = min(n_first + i, n_out - 1);       // (a row past the end repeats the last one; it is not stored)
+        wv[i] = __ldg(reinterpret_cast<const uint4*>(we + ((size_t)a * n_out + n) * k_dim) + c);
+      }
+#pragma unroll
+      for (int i = 0; i < PER_WARP; ++i) {
+        float f[8];
+        moe_unpack8(wv[i], f);
+#pragma unroll
+        for (int r = 0; r < MOE_FEW; ++r) {
+          if (r < nr) {
+            const float4 p = xv[r][0], q = xv[r][1];
+            acc[a][i][r] += f[0] * p.x + f[1] * p.y + f[2] * p.z + f[3] * p.w + f[4] * q.x + f[5] * q.y + f[6] * q.z + f[7] * q.w;
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < NW; ++a)
+#pragma unroll
+    for (int i = 0; i < PER_WARP; ++i)
+#pragma unroll
+      for (int r = 0; r < MOE_FEW; ++r) acc[a][i][r] = warp_sum(acc[a][i][r]);
+  // lane 4 i + r files weight row i for the tile's row r
+  float v0 = 0.f, v1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER_WARP; ++i)
+#pragma unroll
+    for (int r = 0; r < MOE_FEW; ++r)
+      if (lane == i * MOE_FEW + r) { v0 = acc[0][i][r]; v1 = acc[NW - 1][i][r]; }
+  static_assert(PER_WARP * MOE_FEW == 32, "a lane for every (weight row, tile row)");
+  const int n = n_first + lane / MOE_FEW, r = lane % MOE_FEW;
+  if (n < n_out && r < nr) {
+    if (MODE == 1) {
+      const float g = fminf(rnd<bf16>(v0), limit);
+      const float u = fminf(fmaxf(rnd<bf16>(v1), -limit), limit);
+      y[((size_t)tile * MOE_FEW + r) * n_out + n] = from_f<bf16>(g / (1.f + expf(-1.702f * g)) * (u + 1.f));
+    } else if (MODE == 2) {
+      const float u = fmaxf(rnd<bf16>(v0), 0.f);
+      y[((size_t)tile * MOE_FEW + r) * n_out + n] = from_f<bf16>(u * u);
+    } else {
+      y[(size_t)src[r] * n_out + n] = from_f<bf16>(v0);
+    }
+  }
+}
+
 // The rows of h in the order of `sorted` (a pair's row is h[pair / top]; zeros where a tile is padded), for a
 // product that wants its rows in place: a block a row, 16-byte pieces.  Rows behind the last tile stay unwritten.
 __global__ void moe_gather_kernel(const bf16* __restrict__ h, const int* __restrict__ sorted,
@@ -521,6 +667,18 @@ template <int MODE>
 static int moe_tiles_mode(int dtype, int tile_rows, const void* x, const void* w, void* y, const int* sorted,
                           const int* tile_expert, const int* n_tiles, int max_tiles, int k_dim, int n_out, int top,
                           float limit, cudaStream_t s) {
+  if (tile_rows == MOE_FEW) {
+    if (dtype != 1 || k_dim % 8 || k_dim > MOE_FEW_MAX_K || ((uintptr_t)x % 16) || ((uintptr_t)w % 16)) return -2;
+    const size_t smem = (size_t)MOE_FEW * k_dim * sizeof(float);
+    static size_t configured = 0;
+    if (smem > configured) {
+      cudaError_t err = cudaFuncSetAttribute(moe_few_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) return (int)err;
+      configured = smem;
+    }
+    return launch_dependent(moe_few_kernel<MODE>, dim3(max_tiles, (n_out + MOE_FEW_NB - 1) / MOE_FEW_NB), dim3(256), smem, s,
+                            (const bf16*)x, (const bf16*)w, (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
+  }
   if (tile_rows == MOE_BIG) {
     if (dtype != 1 || k_dim % 16 || n_out % 2 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)y % 4)) return -2;
     constexpr int NW = MODE == 1 ? 2 : 1, LD = (NW == 1 ? 64 : 32) + 8;
@@ -533,7 +691,7 @@ static int moe_tiles_mode(int dtype, int tile_rows, const void* x, const void* w
   if (tile_rows == MOE_TC_BM) {
     if (dtype != 1 || k_dim % 16 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16)) return -2;
     constexpr int NW = MODE == 1 ? 2 : 1;
-    const size_t smem = (size_t)3 * (1 + NW) * 64 * 40 * sizeof(bf16) + (size_t)NW * 64 * (MOE_BN + 4) * sizeof(float);
+    const size_t smem = (size_t)3 * (1 + NW) * 64 * (MOE_TC_BK + 8) * sizeof(bf16);
     cudaFuncSetAttribute(moe_tile_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return launch_dependent(moe_tile_tc_kernel<MODE>, grid, dim3(256), smem, s, (const bf16*)x, (const bf16*)w,
                             (bf16*)y, sorted, tile_expert, n_tiles, k_dim, n_out, top, limit);
@@ -554,12 +712,14 @@ int sb_moe_tile_rows(int dtype, int width, int inner) {
   return dtype == 1 && width % 16 == 0 && inner % 16 == 0 ? MOE_TC_BM : MOE_BM;
 }
 // The same for a step of `n_pairs` (row, expert) pairs over `experts` experts: when the tensor-core tiles take
-// the operands, 128 from 128 rows an expert on average (the large tiles pay for their padding from there
+// the operands, 4 up to four rows an expert on average (the few-row kernel), 128 from 128 rows an expert on average (the large tiles pay for their padding from there
 // on) and 256 from 256 (the row tiles of the grouped tcgen05 product, which runs in place of these tiles);
 // else as above.
 int sb_moe_tile_rows_for(int dtype, int width, int inner, long long n_pairs, int experts) {
   const int rows = sb_moe_tile_rows(dtype, width, inner);
   if (rows != MOE_TC_BM) return rows;
+  // 4: the few-row kernel, up to four rows an expert on average (single tokens)
+  if (n_pairs <= (long long)MOE_FEW * experts && width <= MOE_FEW_MAX_K && inner <= MOE_FEW_MAX_K) return MOE_FEW;
   // 256: the grouped tcgen05 product (its row tiles), from 256 rows an expert on average
   if (n_pairs >= 256ll * experts) return 256;
   return n_pairs >= (long long)MOE_BIG * experts ? MOE_BIG : rows;

@@ -1640,9 +1640,9 @@ def moe_experts(h, ids, weights, gate_up, down, limit=0.0, expert="gated_clamped
     gate rows, then its up rows), ``down`` ``[E, W, F]``; an expert is ``down(g * sigmoid(1.702 g) * (u +
     1))`` with ``g = min(gate(h), limit)`` and ``u = clamp(up(h), -limit, limit)``.  With ``expert``
     ``"relu2"`` the experts have no gate: ``gate_up`` is ``[E, F, W]`` and an expert is
-    ``down(relu(up(h))^2)``.  Returns ``[T, W]``.  ``tile_rows`` names the tile kind (32: plain; 64 and 128:
-    ``mma.sync`` tiles; 256: the grouped tcgen05 product over rows gathered in the experts' order) instead of
-    the one the step's shape chooses: 128 from 128 rows an expert on average, 256 from 256.  ``status``: the
+    ``down(relu(up(h))^2)``.  Returns ``[T, W]``.  ``tile_rows`` names the tile kind (32: plain; 4: the few-row kernel;
+    64 and 128: ``mma.sync`` tiles; 256: the grouped tcgen05 product over rows gathered in the experts' order) instead of
+    the one the step's shape chooses: 4 up to four rows an expert on average, 128 from 128, 256 from 256.  ``status``: the
     device word a tcgen05 wait that ran out is noted in."""
     if expert not in MOE_EXPERTS:
         raise KernelError(f"no expert kind {expert!r} (known: {', '.join(MOE_EXPERTS)})")
@@ -1663,7 +1663,7 @@ def moe_experts(h, ids, weights, gate_up, down, limit=0.0, expert="gated_clamped
     # 64 and 128: tensor-core tiles (128 with many rows an expert); 32: the plain ones
     bm = lib.sb_moe_tile_rows_for(_code(h.dtype), width, inner, ctypes.c_longlong(n_pairs), experts)
     if tile_rows is not None:
-        if tile_rows not in (32, 64, 128, 256) or (tile_rows > 32 and lib.sb_moe_tile_rows(_code(h.dtype), width, inner) != 64):
+        if tile_rows not in (4, 32, 64, 128, 256) or (tile_rows != 32 and lib.sb_moe_tile_rows(_code(h.dtype), width, inner) != 64):
             raise KernelError(f"no expert tiles of {tile_rows} rows for {h.dtype}, width {width}, inner size {inner}")
         bm = int(tile_rows)
     max_tiles = -(-n_pairs // bm) + min(experts, n_pairs)

@@ -475,7 +475,7 @@ def test_experts_on_every_tile_kind(experts, top, width, inner):
         used = share > 0
         want[used] += share[used, None] * plain.expert(h64[used], w, "e.", 1.25)
     assert ops._lib("moe").sb_moe_tile_rows_for(1, width, inner, rows * top, experts) in (128, 256)
-    for tile_rows in (None, 32, 64, 128, 256):
+    for tile_rows in (None, 4, 32, 64, 128, 256):
         out = ops.moe_experts(h, ids.cuda(), weights.cuda(), gate_up, down, 1.25, tile_rows=tile_rows)
         close(out, want, "bfloat16", f"tiles of {tile_rows or 'the chosen'} rows")
 

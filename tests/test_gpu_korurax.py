@@ -425,7 +425,7 @@ def test_squared_relu_experts_on_every_tile_kind(experts, top, width, inner, row
         assert ops._lib("moe").sb_moe_tile_rows_for(1, width, inner, rows * top, experts) in (128, 256)
     got = ops.moe_experts(h, dev(ids, torch.int32), dev(weights), up, down, expert="relu2")
     close(got, want, "bfloat16", "the tiles the step chooses", bf16=2.5e-2)
-    for tile_rows in (32, 64, 128, 256):
+    for tile_rows in (4, 32, 64, 128, 256):
         got = ops.moe_experts(h, dev(ids, torch.int32), dev(weights), up, down, expert="relu2", tile_rows=tile_rows)
         close(got, want, "bfloat16", f"tiles of {tile_rows} rows", bf16=2.5e-2)
 
