@@ -35,10 +35,24 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
   const int row = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const T* hr = h + (size_t)row * width;
+  // (16-byte pieces of the router's rows when the rows allow it: a lane's loads are then all in flight together)
+  const bool wide = width % 4 == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)hr % 8) == 0;
   for (int e = warp; e < experts; e += warps) {
     const float* wr = w + (size_t)e * width;
     float a = 0.f;
-    for (int c = lane; c < width; c += 32) a += to_f<T>(hr[c]) * wr[c];
+    if (wide && sizeof(T) == 2) {
+      const float4* w4 = reinterpret_cast<const float4*>(wr);
+      const uint2* h4 = reinterpret_cast<const uint2*>(hr);
+#pragma unroll 4
+      for (int c = lane; c < width / 4; c += 32) {
+        const float4 wv = w4[c];
+        const uint2 hv = h4[c];
+        a += __uint_as_float(hv.x << 16) * wv.x + __uint_as_float(hv.x & 0xffff0000u) * wv.y +
+             __uint_as_float(hv.y << 16) * wv.z + __uint_as_float(hv.y & 0xffff0000u) * wv.w;
+      }
+    } else {
+      for (int c = lane; c < width; c += 32) a += to_f<T>(hr[c]) * wr[c];
+    }
     a = warp_sum(a);
     if (lane == 0) z[e] = a + (b ? b[e] : 0.f);
   }
@@ -745,10 +759,12 @@ int sb_moe_route(int dtype, const void* h, const float* w, const float* b, int* 
   if (experts < 1 || experts > MOE_MAX_EXPERTS || top < 1 || top > MOE_MAX_TOP || top > experts) return -2;
   if (scoring != 0 && scoring != 1) return -2;
   const size_t smem = (size_t)experts * sizeof(float);
+  // a step of few rows leaves most SMs idle: a warp an expert (up to 16) shortens the one block a row
+  const int threads = n_tokens <= 64 ? (experts >= 16 ? 512 : experts > 4 ? 256 : 128) : 128;
   if (dtype == 0)
-    return launch_dependent(moe_route_kernel<float>, dim3(n_tokens), dim3(128), smem, s, (const float*)h, w, b, ids,
+    return launch_dependent(moe_route_kernel<float>, dim3(n_tokens), dim3(threads), smem, s, (const float*)h, w, b, ids,
                             weights, width, experts, top, scoring, weight_scale);
-  return launch_dependent(moe_route_kernel<bf16>, dim3(n_tokens), dim3(128), smem, s, (const bf16*)h, w, b, ids,
+  return launch_dependent(moe_route_kernel<bf16>, dim3(n_tokens), dim3(threads), smem, s, (const bf16*)h, w, b, ids,
                           weights, width, experts, top, scoring, weight_scale);
 }
 
