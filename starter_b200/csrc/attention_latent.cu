@@ -350,7 +350,9 @@ latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, 
   if (b_begin < b_end) load_keys(b_begin, 0);
   cp_async_commit();
 
-  const int wr = warp & 3, wc = warp >> 2;
+  // neighbouring warps are the two halves of a row group, so that the row groups of a block with few rows
+  // (single tokens: `heads` rows of 64) sit on different schedulers
+  const int wr = warp >> 1, wc = warp & 1;
   const int g = lane >> 2, tq = lane & 3;
   const int c_half = (rank / 2 + 15) / 16 * 16;
   const int col_lo = wc == 0 ? 0 : c_half, col_hi = wc == 0 ? c_half : rank;
@@ -369,6 +371,7 @@ latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, 
 #pragma unroll
   for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const bool warp_has_rows = __any_sync(0xffffffffu, row_ok[0] || row_ok[1]);   // else: loads and barriers only
 
   for (int b = b_begin; b < b_end; ++b) {
     const int buf = (b - b_begin) & 1;
@@ -377,6 +380,7 @@ latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, 
     cp_async_wait<1>();
     __syncthreads();
     const bf16* kb = ks + (size_t)buf * LA_BN * ld;
+    if (warp_has_rows) {
     float s[4][4];
 #pragma unroll
     for (int n = 0; n < 4; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
@@ -444,6 +448,7 @@ latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, 
           mma16816(o[2 * pr + 1], pa, vf[2], vf[3]);
         }
       }
+    }
     }
     __syncthreads();
   }
