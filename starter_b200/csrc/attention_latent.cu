@@ -259,6 +259,7 @@ int sb_latent_attention(int dtype, const void* qa, void* out, const void* store,
 // unnormalised sums) per row in scratch memory for latent_merge_kernel: single tokens of few sequences.
 #define LA_BM 64
 #define LA_BN 32
+#define LA_PLD 40      // a row of P: 32 keys and 8 entries of padding (ldmatrix without bank conflicts)
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool real) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -287,6 +288,11 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&p);
 }
 
+// The two warps of a row group meet (named barriers 1 to 4; 0 is the block's).
+__device__ __forceinline__ void pair_sync(int row_group) {
+  asm volatile("bar.sync %0, 64;" ::"r"(row_group + 1) : "memory");
+}
+
 template <int NT>   // 8-column tiles of the latent a warp sums (its half of the value columns, rounded up)
 __global__ void __launch_bounds__(256, 1)
 latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, float* __restrict__ part_acc,
@@ -300,6 +306,8 @@ latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, 
   const int Dk = rank + rot, ld = Dk + 8;
   bf16* qs = reinterpret_cast<bf16*>(latent_smem);
   bf16* ks = qs + LA_BM * ld;
+  bf16* ps = ks + 2 * LA_BN * ld;                                 // [4 row groups][16 rows][LA_PLD]: the weights P
+  float* xm = reinterpret_cast<float*>(ps + 4 * 16 * LA_PLD);     // [4 row groups][2 halves][16 rows]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int per_tile = subs * head_chunks;
   const int tile = blockIdx.x / per_tile, rem = blockIdx.x % per_tile;
@@ -381,51 +389,60 @@ latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, 
     __syncthreads();
     const bf16* kb = ks + (size_t)buf * LA_BN * ld;
     if (warp_has_rows) {
-    float s[4][4];
+    // this warp's half of the block's keys: S = Q K^T for 16 rows x 16 keys
+    float s[2][4];
 #pragma unroll
-    for (int n = 0; n < 4; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
     for (int kk = 0; kk < Dk / 16; ++kk) {
-      unsigned a[4];
+      unsigned a[4], kf[4];
       ldsm4(a, qs + (16 * wr + (lane & 15)) * ld + kk * 16 + (lane >> 4) * 8);
-#pragma unroll
-      for (int np = 0; np < 2; ++np) {
-        unsigned kf[4];
-        const int mi = lane >> 3;
-        ldsm4(kf, kb + (16 * np + (lane & 7) + (mi >> 1) * 8) * ld + kk * 16 + (mi & 1) * 8);
-        mma16816(s[2 * np], a, kf[0], kf[1]);
-        mma16816(s[2 * np + 1], a, kf[2], kf[3]);
-      }
+      const int mi = lane >> 3;
+      ldsm4(kf, kb + (16 * wc + (lane & 7) + (mi >> 1) * 8) * ld + kk * 16 + (mi & 1) * 8);
+      mma16816(s[0], a, kf[0], kf[1]);
+      mma16816(s[1], a, kf[2], kf[3]);
     }
-    // mask by each row's own position and window, running maximum and sum
+    // mask by each row's own position and window; the maximum of the half, then of both halves
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int n = 0; n < 4; ++n)
+    for (int n = 0; n < 2; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int i = e >> 1;
-        const int j = b * LA_BN + n * 8 + 2 * tq + (e & 1);
+        const int j = b * LA_BN + 16 * wc + n * 8 + 2 * tq + (e & 1);
         const bool seen = row_ok[i] && j >= row_lo[i] && j <= row_pos[i];
         s[n][e] = seen ? s[n][e] * scale : -INFINITY;
         mx[i] = fmaxf(mx[i], s[n][e]);
       }
-    float alpha[2], m_use[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
       mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-      const float m_new = fmaxf(m_run[i], mx[i]);
+      if (tq == 0) xm[(wr * 2 + wc) * 16 + g + 8 * i] = mx[i];
+    }
+    pair_sync(wr);
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float m_new = fmaxf(m_run[i], fmaxf(mx[i], xm[(wr * 2 + (wc ^ 1)) * 16 + g + 8 * i]));
       m_use[i] = m_new == -INFINITY ? 0.f : m_new;
       alpha[i] = expf(m_run[i] - m_use[i]);
       m_run[i] = m_new;
       l_run[i] *= alpha[i];
     }
+    // the half's weights: summed here (the halves' sums meet at the end), and left for both halves' P V
 #pragma unroll
-    for (int n = 0; n < 4; ++n)
+    for (int n = 0; n < 2; ++n) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         s[n][e] = expf(s[n][e] - m_use[e >> 1]);
         l_run[e >> 1] += s[n][e];
       }
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        *reinterpret_cast<unsigned*>(ps + (wr * 16 + g + 8 * i) * LA_PLD + 16 * wc + n * 8 + 2 * tq) =
+            pack_bf16(s[n][2 * i], s[n][2 * i + 1]);
+    }
+    pair_sync(wr);
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
       o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
@@ -434,10 +451,7 @@ latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, 
 #pragma unroll
     for (int k2 = 0; k2 < 2; ++k2) {
       unsigned pa[4];
-      pa[0] = pack_bf16(s[2 * k2][0], s[2 * k2][1]);
-      pa[1] = pack_bf16(s[2 * k2][2], s[2 * k2][3]);
-      pa[2] = pack_bf16(s[2 * k2 + 1][0], s[2 * k2 + 1][1]);
-      pa[3] = pack_bf16(s[2 * k2 + 1][2], s[2 * k2 + 1][3]);
+      ldsm4(pa, ps + (wr * 16 + (lane & 15)) * LA_PLD + k2 * 16 + (lane >> 4) * 8);
 #pragma unroll
       for (int pr = 0; pr < NT / 2; ++pr) {
         if (pr < n_pairs) {
@@ -454,10 +468,16 @@ latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, 
   }
   cp_async_wait<0>();
   pdl_trigger();
+  if (warp_has_rows) {
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
-    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    for (int i = 0; i < 2; ++i) {
+      l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+      l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+      if (tq == 0) xm[(wr * 2 + wc) * 16 + g + 8 * i] = l_run[i];
+    }
+    pair_sync(wr);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) l_run[i] += xm[(wr * 2 + (wc ^ 1)) * 16 + g + 8 * i];
   }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -534,7 +554,7 @@ int sb_latent_attention_tc(const void* qa, void* out, float* part_acc, float* pa
   const int tile_tokens = max_q_len > 0 && max_q_len < 64 ? max_q_len : 64;
   const int subs = (tile_tokens + tokens_per_block - 1) / tokens_per_block;
   const int ld = rank + rot + 8;
-  const size_t smem = (size_t)(LA_BM + 2 * LA_BN) * ld * sizeof(bf16);
+  const size_t smem = (size_t)(LA_BM + 2 * LA_BN) * ld * sizeof(bf16) + 4 * 16 * LA_PLD * sizeof(bf16) + 4 * 2 * 16 * sizeof(float);
   const dim3 grid(n_tiles * subs * head_chunks, n_splits);
   const int c_half = (rank / 2 + 15) / 16 * 16;
   const int nt = c_half / 8;

@@ -457,6 +457,38 @@ def test_each_request_alone_and_whole(tmp_path_factory, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_long_prompts_of_a_wider_model(tmp_path_factory, dtype):
+    """Prompts of hundreds of tokens on a wider model, where a step's shape chooses the large tiles (hundreds of
+    rows an expert, keys and values of 128): whole, then the same request as a long portion, a short one and
+    single tokens, next to a second request."""
+    from starter_b200.engine import StepEntry
+
+    _, cfg, w = case(tmp_path_factory, "RD")
+    routed = Routed(runner_for(tmp_path_factory, "RD", dtype))
+    runner = routed.runner
+    prompt, other = random_prompt(700, cfg["vocab"], 71), random_prompt(333, cfg["vocab"], 72)
+    slot = runner.open_sequence()
+    got = routed.step([StepEntry(slot, prompt, all_places(700))], ["whole"])
+    runner.close_sequence(slot)
+    want = plain.forward(cfg, w, prompt, expert_ids=routed.routes("whole", dtype))
+    assert_close(got, want, dtype, "RD whole, 700 tokens")
+    a, b = runner.open_sequence(), runner.open_sequence()
+    rows = [routed.step([StepEntry(a, prompt[:600], all_places(600)), StepEntry(b, other, all_places(333))], ["a", "b"])]
+    got_b = rows[0][600:]
+    rows = [rows[0][:600], routed.step([StepEntry(a, prompt[600:690], all_places(90))], ["a"])]
+    runner.close_sequence(b)
+    for tok in prompt[690:]:
+        rows.append(routed.step([StepEntry(a, [tok], [0])], ["a"]))
+    runner.close_sequence(a)
+    assert_close(torch.cat(rows), plain.forward(cfg, w, prompt, expert_ids=routed.routes("a", dtype)), dtype,
+                 "RD in portions of 600, 90 and single tokens")
+    assert_close(got_b, plain.forward(cfg, w, other, expert_ids=routed.routes("b", dtype)), dtype,
+                 "RD: the request beside it")
+    runner.check_status()
+    runner.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", CONFIGS)
 def test_every_layer_against_the_plain_layers(tmp_path_factory, name, dtype):
     """The stream behind each layer (summed over depth), which names the first layer that differs."""
