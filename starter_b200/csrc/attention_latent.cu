@@ -251,10 +251,12 @@ int sb_latent_attention(int dtype, const void* qa, void* out, const void* store,
 // The same attention for bfloat16 on mma.sync tiles (rank and rot multiples of 16).  A block owns up to
 // 64 query rows: the heads (up to 64 of them) of consecutive tokens of one sequence, which all score the
 // same cache rows.  It walks the keys its tokens can see in blocks of 32 (a block of keys never leaves a
-// page), double-buffered by cp.async; eight warps = four groups of 16 query rows times two halves of the
-// value columns.  Both halves form the same scores S = Q K^T (16 x 32 a warp, float), mask them by each
-// row's own position and window, keep the running maximum and sum per row, and add P V for their half of
-// the latent's columns, V being the first `rank` entries of the very key rows in shared memory.
+// page), double-buffered by cp.async; eight warps = four groups of 16 query rows times two halves.  A warp
+// forms the scores S = Q K^T of its half of the block's keys (16 x 16, float), masks them by each row's own
+// position and window, and meets the other half through shared memory (the halves' row maxima, then the
+// weights P in bfloat16) behind a named barrier of the pair; each half keeps the running maximum, the sum of
+// its own keys' weights (the sums meet at the end), and adds P V for its half of the latent's columns, V
+// being the first `rank` entries of the very key rows in shared memory.
 // With n_splits > 1 the key blocks are dealt out to gridDim.y blocks, which leave (maximum, sum,
 // unnormalised sums) per row in scratch memory for latent_merge_kernel: single tokens of few sequences.
 #define LA_BM 64
