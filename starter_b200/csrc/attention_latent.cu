@@ -454,14 +454,26 @@ latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, 
     for (int k2 = 0; k2 < 2; ++k2) {
       unsigned pa[4];
       ldsm4(pa, ps + (wr * 16 + (lane & 15)) * LA_PLD + k2 * 16 + (lane >> 4) * 8);
+      const bf16* v_at = kb + (16 * k2 + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + col_lo + (lane >> 4) * 8;
+      if (n_pairs == NT / 2) {
+        // every tile of the template's count is real (the usual case): no branch between the tiles, so that
+        // the loads of the tiles ahead are in flight while a tile multiplies
 #pragma unroll
-      for (int pr = 0; pr < NT / 2; ++pr) {
-        if (pr < n_pairs) {
+        for (int pr = 0; pr < NT / 2; ++pr) {
           unsigned vf[4];
-          const int mi = lane >> 3;
-          ldsm4_t(vf, kb + (16 * k2 + (lane & 7) + (mi & 1) * 8) * ld + col_lo + pr * 16 + (mi >> 1) * 8);
+          ldsm4_t(vf, v_at + pr * 16);
           mma16816(o[2 * pr], pa, vf[0], vf[1]);
           mma16816(o[2 * pr + 1], pa, vf[2], vf[3]);
+        }
+      } else {
+#pragma unroll
+        for (int pr = 0; pr < NT / 2; ++pr) {
+          if (pr < n_pairs) {
+            unsigned vf[4];
+            ldsm4_t(vf, v_at + pr * 16);
+            mma16816(o[2 * pr], pa, vf[0], vf[1]);
+            mma16816(o[2 * pr + 1], pa, vf[2], vf[3]);
+          }
         }
       }
     }
