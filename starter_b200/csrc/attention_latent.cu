@@ -338,15 +338,23 @@ latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, 
   const int b_begin = b_lo + split * per_split, b_end = min(b_lo + n_blocks, b_begin + per_split);
   const int chunks = Dk / 8;                      // 16-byte pieces of a row
 
+  // A thread's pieces of a key block: piece tid + 256 k is piece c of row kr, found once here and stepped by
+  // k; a block of 32 keys lies in one page, whose number is looked up once a block.
+  static_assert(SB_PAGE_TOKENS % LA_BN == 0, "a block of keys must not leave a page");
+  const int kr0 = tid / chunks, c0 = tid - kr0 * chunks;
+  const int step_r = 256 / chunks, step_c = 256 - step_r * chunks;
   auto load_keys = [&](int b, int buf) {
     bf16* dst = ks + (size_t)buf * LA_BN * ld;
-    for (int i = tid; i < LA_BN * chunks; i += 256) {
-      const int kr = i / chunks, c = i - kr * chunks;
-      const int j = b * LA_BN + kr;
-      const bool real = j <= p_last;
-      const int jj = real ? j : p_last;
-      const bf16* src = store + ((size_t)pages[jj / SB_PAGE_TOKENS] * SB_PAGE_TOKENS + jj % SB_PAGE_TOKENS) * Dk + c * 8;
-      cp_async16(dst + kr * ld + c * 8, src, real);
+    const int j0 = b * LA_BN;
+    const bf16* src0 = store + ((size_t)pages[j0 / SB_PAGE_TOKENS] * SB_PAGE_TOKENS + j0 % SB_PAGE_TOKENS) * Dk;
+    int kr = kr0, c = c0;
+    while (kr < LA_BN) {
+      const bool real = j0 + kr <= p_last;
+      const int rr = real ? kr : p_last - j0;       // (a key of the same block stands in; nothing is copied)
+      cp_async16(dst + kr * ld + c * 8, src0 + (size_t)rr * Dk + c * 8, real);
+      kr += step_r;
+      c += step_c;
+      if (c >= chunks) { c -= chunks; ++kr; }
     }
   };
   // the queries, and the first block of keys
@@ -445,10 +453,12 @@ latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, 
             pack_bf16(s[n][2 * i], s[n][2 * i + 1]);
     }
     pair_sync(wr);
+    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {   // (no row's maximum moved: nothing to rescale)
 #pragma unroll
-    for (int n = 0; n < NT; ++n) {
-      o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
-      o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+      for (int n = 0; n < NT; ++n) {
+        o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+        o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+      }
     }
 #pragma unroll
     for (int k2 = 0; k2 < 2; ++k2) {
