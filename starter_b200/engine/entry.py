@@ -11,6 +11,8 @@ temperature, seeds, stop tokens, early finish and several batches.
 
 from __future__ import annotations
 
+import sys
+
 import torch
 
 from ..cache.layout import PAGE_TOKENS
@@ -59,7 +61,7 @@ class Engine:
         small = cache is not None and self._fixed_tokens is None and (
             need > cache.num_pages * PAGE_TOKENS or pages[0] > cache.max_pages_per_sequence)
         if cache is None or small:
-            print(f"[engine] building the cache for {need} tokens", flush=True)
+            print(f"[engine] building the cache for {need} tokens", file=sys.stderr, flush=True)
             self._build_runner(max(need, PAGE_TOKENS), None if self._fixed_tokens else pages[0] * PAGE_TOKENS)
         return GenerationLoop(self.runner, self.sampler, batch, self.runner.cache.num_pages)
 
