@@ -1,6 +1,6 @@
 """Pre-norm layers around a float32 residual stream that is joined over depth.
 
-With ``X_0`` the embedding output and ``X_(i+1)`` the result of layer ``i``,
+Level 0 of the history is the token embedding (``X_0``); layer ``i`` files its result as level ``i + 1``:
 
     x1 = x + m * mixer(norm1(x)),   X_(i+1) = x1 + m * feed_forward(norm2(x1)),   x <- sum_(j <= i+1) a_i[j] X_j
 
