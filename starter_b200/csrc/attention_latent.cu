@@ -532,27 +532,40 @@ latent_attention_tc_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out, 
   }
 }
 
-// out[row] = sum_s acc[s][row] exp(m_s - M) / sum_s l_s exp(m_s - M): a block a row.
+// out[row] = sum_s acc[s][row] exp(m_s - M) / sum_s l_s exp(m_s - M): a block a row.  The first warp forms
+// the parts' factors (a lane a part, up to 32 parts) and leaves them in shared memory; the sums over the
+// parts then run without a branch, their loads independent of one another.
 __global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, int n_rows, int rank, int n_splits) {
+  __shared__ float factor[32];
   pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(part_acc);
   SB_BEHIND_WAIT(part_ml);
   const int row = blockIdx.x;
-  float M = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[((size_t)s * n_rows + row) * 2]);
-  float L = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float m = part_ml[((size_t)s * n_rows + row) * 2];
-    if (m != -INFINITY) L += part_ml[((size_t)s * n_rows + row) * 2 + 1] * expf(m - M);
+  if (threadIdx.x < 32) {
+    const int s = threadIdx.x;
+    const bool has = s < n_splits;
+    const float m = has ? part_ml[((size_t)s * n_rows + row) * 2] : -INFINITY;
+    const float l = has ? part_ml[((size_t)s * n_rows + row) * 2 + 1] : 0.f;
+    float M = m;
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    const float e = m == -INFINITY ? 0.f : expf(m - M);
+    float L = l * e;
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    factor[s] = e / L;
   }
+  __syncthreads();
+  const float* acc = part_acc + (size_t)row * rank;
+  const size_t part_stride = (size_t)n_rows * rank;
   for (int c = threadIdx.x; c < rank; c += blockDim.x) {
     float a = 0.f;
+#pragma unroll 8
     for (int s = 0; s < n_splits; ++s) {
-      const float m = part_ml[((size_t)s * n_rows + row) * 2];
-      if (m != -INFINITY) a += part_acc[((size_t)s * n_rows + row) * rank + c] * expf(m - M);
+      const float f = factor[s];
+      const float v = acc[s * part_stride + c];
+      a += f != 0.f ? v * f : 0.f;          // (a part without keys left zeros; its factor is zero)
     }
-    out[(size_t)row * rank + c] = from_f<bf16>(a / L);
+    out[(size_t)row * rank + c] = from_f<bf16>(a);
   }
 }
 
@@ -570,7 +583,7 @@ int sb_latent_attention_tc(const void* qa, void* out, float* part_acc, float* pa
                            int n_tiles, int n_tokens, int heads, int rank, int rot, float scale, int window, int n_splits,
                            int max_q_len, cudaStream_t s) {
   if (n_tiles == 0 || n_tokens == 0) return 0;
-  if (rank % 16 || rot % 16 || rank < 16 || rank > 512 || rank + rot > 640 || n_splits < 1) return -2;
+  if (rank % 16 || rot % 16 || rank < 16 || rank > 512 || rank + rot > 640 || n_splits < 1 || n_splits > 32) return -2;
   const int heads_per_block = heads < 64 ? heads : 64;
   const int tokens_per_block = 64 / heads_per_block;
   const int head_chunks = (heads + heads_per_block - 1) / heads_per_block;
