@@ -51,15 +51,20 @@ BF16_ROW_TOL = 5e-2
 BF16_MEAN_TOL = 8e-3
 
 
-def assert_close(got, want, dtype, what=""):
+def assert_close(got, want, dtype, what="", stray=0.0):
     """Fails with the first wrong row named: its place is the clue (a prompt's end, the first single-token
-    step, a page boundary, a chunk's edge)."""
+    step, a page boundary, a chunk's edge).  ``stray`` (bfloat16 only, for comparisons of hundreds of rows):
+    the share of rows that may pass the row bound, none of them by more than twice; among hundreds of rows the
+    tail of bfloat16 rounding (one sharp softmax) reaches further than among a tiny case's dozens, while a
+    lost key or a misplaced tile moves whole runs of rows, and by far more.  float32 holds every row."""
     got, want = got.detach().double().cpu(), want.detach().double().cpu()
     assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
     scale = float(want.abs().max())
     tol = (FP32_TOL if dtype == "float32" else BF16_ROW_TOL) * scale
     err = (got - want).abs().reshape(want.shape[0], -1).max(dim=1).values
     bad = (~(err <= tol)).nonzero().flatten().tolist()
+    if dtype != "float32" and stray > 0.0 and len(bad) <= stray * len(err) and float(err.max()) <= 2.0 * tol:
+        bad = []
     assert not bad, (f"{what}: {len(bad)} of {len(err)} rows off by more than {tol:.2e}; first wrong row {bad[0]} "
                      f"(error {err[bad[0]].item():.3e}), largest error {err.max().item():.3e}")
     if dtype != "float32":
@@ -471,7 +476,7 @@ def test_long_prompts_of_a_wider_model(tmp_path_factory, dtype):
     got = routed.step([StepEntry(slot, prompt, all_places(700))], ["whole"])
     runner.close_sequence(slot)
     want = plain.forward(cfg, w, prompt, expert_ids=routed.routes("whole", dtype))
-    assert_close(got, want, dtype, "RD whole, 700 tokens")
+    assert_close(got, want, dtype, "RD whole, 700 tokens", stray=0.01)
     a, b = runner.open_sequence(), runner.open_sequence()
     rows = [routed.step([StepEntry(a, prompt[:600], all_places(600)), StepEntry(b, other, all_places(333))], ["a", "b"])]
     got_b = rows[0][600:]
@@ -481,9 +486,9 @@ def test_long_prompts_of_a_wider_model(tmp_path_factory, dtype):
         rows.append(routed.step([StepEntry(a, [tok], [0])], ["a"]))
     runner.close_sequence(a)
     assert_close(torch.cat(rows), plain.forward(cfg, w, prompt, expert_ids=routed.routes("a", dtype)), dtype,
-                 "RD in portions of 600, 90 and single tokens")
+                 "RD in portions of 600, 90 and single tokens", stray=0.01)
     assert_close(got_b, plain.forward(cfg, w, other, expert_ids=routed.routes("b", dtype)), dtype,
-                 "RD: the request beside it")
+                 "RD: the request beside it", stray=0.01)
     runner.check_status()
     runner.cache.check()
 

@@ -56,10 +56,10 @@ R_C = dict(architecture="Korurax", vocab=257, width=128, norm=dict(eps=1e-5), re
 # wider, for prompts of hundreds of tokens: keys and values of 128 (the tcgen05 prompt kernel at its larger head
 # size), few experts (hundreds of rows an expert: the grouped tcgen05 product) next to more (the 128-row tiles),
 # a latent of 256 with a rotated part of 32, chunks of 300 and 97
-R_D = dict(architecture="Korurax", vocab=500, width=256, norm=dict(eps=1e-5), residual_mult=0.4, logit_softcap=80.0, layers=[
+R_D = dict(architecture="Korurax", vocab=500, width=320, norm=dict(eps=1e-5), residual_mult=0.4, logit_softcap=80.0, layers=[
     attention(8, 2, 128, 128, 0.09, 300, moe(4, 2, 128, 1.5)),
     latent(8, 64, 32, 64, 96, 256, 0.1, 500000.0, dense(640, 3.0)),
-    attention(4, 4, 64, 64, 0.125, 97, moe(8, 2, 96, 2.0)),
+    attention(4, 4, 64, 64, 0.11, 97, moe(8, 2, 80, 2.0)),
     latent(2, 48, 16, 32, 64, 64, 0.125, 10000.0, None),
 ])
 
