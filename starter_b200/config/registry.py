@@ -10,6 +10,7 @@ from __future__ import annotations
 import json
 import os
 
+from .bavedra import BavedraConfig
 from .goguvik import GoguvikConfig
 from .kesedra import KesedraConfig
 from .korurax import KoruraxConfig
@@ -29,6 +30,7 @@ register_architecture(Qwen3Config.architecture, Qwen3Config)
 register_architecture(GoguvikConfig.architecture, GoguvikConfig)
 register_architecture(KesedraConfig.architecture, KesedraConfig)
 register_architecture(KoruraxConfig.architecture, KoruraxConfig)
+register_architecture(BavedraConfig.architecture, BavedraConfig)
 
 
 def architecture_name(raw: dict):

@@ -19,12 +19,14 @@ from typing import Optional
 @dataclass(frozen=True)
 class NormSpec:
     """Root-mean-square norm ``x / sqrt(mean(x^2) + eps) * gain``.  ``unit_offset`` false: the stored
-    weight is the gain; true: the weight is stored around zero and the gain is ``1 + weight``."""
+    weight is the gain; true: the weight is stored around zero and the gain is ``1 + weight``.  ``gain_32bit``: the
+    gain is held in float32 on the device however it is stored (for kernels that norm a float32 stream)."""
 
     size: int
     eps: float
     kind: str = "rmsnorm"
     unit_offset: bool = False
+    gain_32bit: bool = False
 
 
 @dataclass(frozen=True)
@@ -144,7 +146,12 @@ class SinkAttentionSpec:
     that many keys, its own included.  ``sink``: the softmax's denominator holds one more term
     ``exp(sink_h)`` (a learnt number per head) that has no value.  ``head_gate``: a head's output is
     multiplied by ``sigmoid(g_h . x)``, one learnt vector per head, read from the mixer's own input.
-    Keys have ``head_dim`` entries, values ``value_dim``."""
+    Keys have ``head_dim`` entries, values ``value_dim``.
+
+    ``fixed_sink`` (a number; needs ``sink`` false): the extra term is ``exp(fixed_sink)`` for every head and the
+    layer has no sink tensor.  ``position`` (an ``InterleavedRopeSpec``): queries and keys are turned by their
+    positions before they are scored.  ``values_from_keys``: the layer has no value projection; a key/value head's
+    value is its key as projected, before any rotation (``value_dim`` = ``head_dim``)."""
 
     hidden_size: int
     num_heads: int
@@ -158,6 +165,8 @@ class SinkAttentionSpec:
     chunk: Optional[int] = None
     window: Optional[int] = None
     position: Optional[object] = None
+    fixed_sink: Optional[float] = None
+    values_from_keys: bool = False
     kind: str = "sink_attention"
 
 
@@ -208,13 +217,87 @@ class WkvSpec:
 
 
 @dataclass(frozen=True)
+class GatedLinearRecurrenceSpec:
+    """Two branches of ``width`` channels: ``y = gelu_tanh(W_y h + b_y)`` and ``u = conv(W_x h + b_x)``, a causal
+    convolution per channel over ``conv`` taps with a bias.  ``u`` in ``blocks`` equal parts, each with two square
+    matrices and biases: ``r = sigmoid(ra u + b)``, ``i = sigmoid(ri u + b)``; per channel ``a = exp(-decay_scale * r *
+    softplus(lam))`` and the state ``S <- a S + sqrt(1 - a^2) i u`` from zero, every token alike; the output is
+    ``W_o (S * y)``.  The state and the convolution's last ``conv - 1`` inputs are kept per sequence in 32-bit."""
+
+    hidden_size: int
+    width: int
+    blocks: int
+    conv: int
+    decay_scale: float = 8.0
+    kind: str = "gated_linear_recurrence"
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec:
+    """A selective state-space recurrence with a ``state x head_dim`` matrix per head.  One projection gives ``[z |
+    x | B | C | dt]`` (``inner = heads * head_dim`` gate entries, as many inputs, ``groups * state`` entries each of B
+    and C, a step per head); x, B and C pass a causal convolution per channel (``conv`` taps, bias) and silu; ``dt <-
+    softplus(dt + dt_bias)``; per head (its group: ``head / (heads / groups)``) ``S <- exp(-exp(A_log) dt) S + dt B
+    x^T``, ``y = S^T C + D x``; ``y * silu(z)`` is RMS-normed in ``norm_groups`` equal parts with a gain, then the
+    output projection.  State and convolution inputs are kept per sequence in 32-bit."""
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    state: int
+    groups: int
+    conv: int
+    norm_groups: int
+    norm_eps: float
+    kind: str = "state_space"
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """The gated delta rule with a ``head_dim x value_dim`` matrix per head.  Queries and keys have ``num_kv_heads``
+    heads (value head ``h`` reads ``h / (num_heads / num_kv_heads)``); q, k and v each pass a causal convolution per
+    channel (``conv`` taps, no bias) and silu; q and k are made unit vectors per head (``x / sqrt(sum x^2 + 1e-6)``),
+    q times ``head_dim ** -0.5``; ``beta = sigmoid(W_b h)``, ``g = exp(-exp(A_log) softplus(W_a h + dt_bias))`` per
+    head; per token ``S <- g S``, ``u = beta (v - S^T k)``, ``S <- S + k u^T``, ``o = S^T q``; each head's ``o`` is
+    RMS-normed with a gain of ``value_dim`` entries shared by the heads and multiplied by ``silu(W_g h)``, then the
+    output projection."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    conv: int
+    norm_eps: float
+    kind: str = "gated_delta"
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Two mixers side by side that read the same input: the result is half the sum of their outputs, each first
+    RMS-normed over the model width with a plain gain of its own."""
+
+    hidden_size: int
+    left: object
+    right: object
+    norm_eps: float
+    kind: str = "parallel"
+
+    @property
+    def position(self):
+        """The position spec of the side that has one (the model builds the tables from it)."""
+        return getattr(self.left, "position", None) or getattr(self.right, "position", None)
+
+
+@dataclass(frozen=True)
 class BiasedFeedForwardSpec:
     """Dense feed-forward with biases on both projections: ``down(act(up(x) + b_up)) + b_down``;
-    ``activation`` ``"relu2"`` is the square of relu."""
+    ``activation`` ``"relu2"`` is the square of relu.  ``bias`` false: no biases, ``down(act(up(x)))``."""
 
     hidden_size: int
     intermediate_size: int
     activation: str = "relu2"
+    bias: bool = True
     kind: str = "dense_biased"
 
 
@@ -227,7 +310,17 @@ class RoutedExpertsSpec:
     ``"sigmoid_normalised"``: the chosen experts' ``sigmoid(logit)`` divided by their sum (+ 1e-20), times
     ``weight_scale``.  ``expert`` ``"gated_clamped"``: ``down(g * sigmoid(1.702 g) * (u + 1))`` with ``g =
     min(gate(x), limit)``, ``u = clamp(up(x), -limit, limit)``; ``"relu2"``: ``down(relu(up(x))^2)``, no gate
-    and no limit."""
+    and no limit; ``"gated_silu"``: ``down(silu(gate(x)) * up(x))``, no limit.
+
+    ``scoring`` ``"softmax_all"``: the scores are the softmax over ALL router outputs; the choice goes by
+    ``score + correction`` (a stored vector, ``correction`` true) among the experts of the ``group_keep`` of
+    ``group_count`` equal groups of neighbouring experts whose largest such number is largest (``group_count`` 1:
+    among all); the weights are the chosen experts' plain scores over their sum (+ 1e-20), times ``weight_scale``.
+
+    ``identity_experts``: the router has that many outputs more than there are experts; one of those, chosen,
+    stands for an expert that hands its input on (times its weight) and has no tensors.  Groups are formed over
+    experts and identity experts together.  ``shared_size`` > 0: a gated expert of that inner size (``"gated_silu"``
+    form) runs for every token and is added times ``sigmoid(sg . x)``, one learnt vector."""
 
     hidden_size: int
     intermediate_size: int
@@ -238,6 +331,11 @@ class RoutedExpertsSpec:
     scoring: str = "softmax_top"
     weight_scale: float = 1.0
     router_bias: bool = True
+    correction: bool = False
+    group_count: int = 1
+    group_keep: int = 1
+    identity_experts: int = 0
+    shared_size: int = 0
     kind: str = "routed_experts"
 
 
@@ -338,6 +436,14 @@ def prenorm_layer(mixer, feed_forward, norm1, norm2, names, arrangement: str = "
     """The layer of the pre-norm block: ``x + mixer(norm1(x))``, then ``+ feed_forward(norm2(.))``."""
     return LayerSpec({"mixer": mixer, "feed_forward": feed_forward, "norm1": norm1, "norm2": norm2},
                      names, arrangement)
+
+
+def prenorm32_layer(mixer, feed_forward, norm1, norm2, names) -> LayerSpec:
+    """The pre-norm layer around a residual stream that is a 32-bit sum: ``x + mixer(norm1(x))``, then ``+
+    feed_forward(norm2(.))``; ``feed_forward`` (and ``norm2``) None: the layer is its mixer alone."""
+    if feed_forward is None:
+        return LayerSpec({"mixer": mixer, "norm1": norm1}, names, "prenorm32_mixer_only")
+    return LayerSpec({"mixer": mixer, "feed_forward": feed_forward, "norm1": norm1, "norm2": norm2}, names, "prenorm32")
 
 
 @dataclass(frozen=True)

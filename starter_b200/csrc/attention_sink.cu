@@ -73,6 +73,68 @@ __global__ void sink_prepare_kernel(const T* __restrict__ proj, int proj_width, 
       gate[(size_t)row * heads + h] = 1.f / (1.f + expf(-to_f<T>(pr[g_at + h])));
 }
 
+// The same for a layer whose queries and keys are turned by their positions and whose values may be its keys:
+// proj: a row = [q (heads * dim) | k (kv_heads * dim) | v (kv_heads * vdim), absent with v_from_k].  The first
+// `rot` entries of every query and key head turn, entry 2i with entry 2i + 1, by the angle whose cos and sin
+// stand at [position][i] of the float tables (rot / 2 columns; rot 0: nothing turns).  Queries are turned in
+// place; keys go to the cache turned, values as they are; with v_from_k a key/value head's value is its key
+// as projected, before the turn (vdim == dim).  A thread a pair of entries; the products are float.
+template <typename T>
+__global__ void sink_prepare_rot_kernel(T* __restrict__ proj, int proj_width, const int* __restrict__ tok_pos,
+                                        const int* __restrict__ tok_slot, const int* __restrict__ block_table,
+                                        int table_stride, T* __restrict__ k_store, T* __restrict__ v_store,
+                                        const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
+                                        int heads, int kv_heads, int dim, int vdim, int v_from_k, int write) {
+  pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
+  SB_BEHIND_WAIT(proj);
+  SB_BEHIND_WAIT(tok_pos);
+  SB_BEHIND_WAIT(tok_slot);
+  SB_BEHIND_WAIT(block_table);
+  const int row = blockIdx.x;
+  T* pr = proj + (size_t)row * proj_width;
+  const int pos = tok_pos[row];
+  const float* cr = cos_t + (size_t)pos * (rot / 2);
+  const float* sr = sin_t + (size_t)pos * (rot / 2);
+  const int half = (dim + 1) / 2;           // pairs a head (the last may be a single entry)
+  for (int e = threadIdx.x; e < heads * half; e += blockDim.x) {
+    const int h = e / half, i = e - h * half;
+    if (2 * i + 1 >= dim || 2 * i >= rot) continue;
+    T* at = pr + (size_t)h * dim + 2 * i;
+    const float a = to_f<T>(at[0]), b = to_f<T>(at[1]), c = cr[i], s = sr[i];
+    at[0] = from_f<T>(a * c - b * s);
+    at[1] = from_f<T>(b * c + a * s);
+  }
+  if (!write) return;
+  const int page = block_table[(size_t)tok_slot[row] * table_stride + pos / SB_PAGE_TOKENS];
+  const int off = pos % SB_PAGE_TOKENS;
+  const T* k = pr + (size_t)heads * dim;
+  const T* v = k + (size_t)kv_heads * dim;
+  for (int e = threadIdx.x; e < kv_heads * half; e += blockDim.x) {
+    const int h = e / half, i = e - h * half;
+    const bool two = 2 * i + 1 < dim;
+    const float a = to_f<T>(k[(size_t)h * dim + 2 * i]), b = two ? to_f<T>(k[(size_t)h * dim + 2 * i + 1]) : 0.f;
+    T* kd = k_store + page_row(page, h, off, kv_heads, dim) + 2 * i;
+    if (two && 2 * i < rot) {
+      const float c = cr[i], s = sr[i];
+      kd[0] = from_f<T>(a * c - b * s);
+      kd[1] = from_f<T>(b * c + a * s);
+    } else {
+      kd[0] = from_f<T>(a);
+      if (two) kd[1] = from_f<T>(b);
+    }
+    if (v_from_k) {
+      T* vd = v_store + page_row(page, h, off, kv_heads, vdim) + 2 * i;
+      vd[0] = from_f<T>(a);
+      if (two) vd[1] = from_f<T>(b);
+    }
+  }
+  if (!v_from_k)
+    for (int e = threadIdx.x; e < kv_heads * vdim; e += blockDim.x) {
+      const int h = e / vdim, d = e - h * vdim;
+      v_store[page_row(page, h, off, kv_heads, vdim) + d] = v[e];
+    }
+}
+
 template <typename T>
 __global__ void sink_attention_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out,
                                       const T* __restrict__ k_store, const T* __restrict__ v_store,
@@ -187,6 +249,25 @@ int sb_sink_prepare(int dtype, const void* proj, int proj_width, const int* tok_
   return launch_dependent(sink_prepare_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, (const bf16*)proj, proj_width,
                           tok_pos, tok_slot, block_table, table_stride, (bf16*)k_store, (bf16*)v_store, gate, heads,
                           kv_heads, dim, vdim, write, vec);
+}
+
+// proj: [n_tokens, proj_width], its queries turned in place; cos_t, sin_t: float [positions, rot / 2] (unused with
+// rot 0); v_from_k: the row has no values and the keys as projected are filed as values (vdim == dim).
+int sb_sink_prepare_rot(int dtype, void* proj, int proj_width, const int* tok_pos, const int* tok_slot,
+                        const int* block_table, int table_stride, void* k_store, void* v_store, const float* cos_t,
+                        const float* sin_t, int rot, int n_tokens, int heads, int kv_heads, int dim, int vdim,
+                        int v_from_k, int write, cudaStream_t s) {
+  if (n_tokens == 0) return 0;
+  if (rot < 0 || rot % 2 || rot > dim || (v_from_k && vdim != dim)) return -2;
+  if (proj_width < heads * dim + (write ? kv_heads * (dim + (v_from_k ? 0 : vdim)) : 0)) return -2;
+  const int threads = heads * dim > 1024 ? 256 : 128;
+  if (dtype == 0)
+    return launch_dependent(sink_prepare_rot_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (float*)proj, proj_width,
+                            tok_pos, tok_slot, block_table, table_stride, (float*)k_store, (float*)v_store, cos_t, sin_t,
+                            rot, heads, kv_heads, dim, vdim, v_from_k, write);
+  return launch_dependent(sink_prepare_rot_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, (bf16*)proj, proj_width,
+                          tok_pos, tok_slot, block_table, table_stride, (bf16*)k_store, (bf16*)v_store, cos_t, sin_t, rot,
+                          heads, kv_heads, dim, vdim, v_from_k, write);
 }
 
 // q: rows of q_stride entries whose first heads * dim are the queries; out: [n_tokens, heads * vdim].

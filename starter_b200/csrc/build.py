@@ -56,6 +56,8 @@ SOURCES = (
     "depth",
     "attention_sink",
     "attention_sink_tc",
+    "short_conv",
+    "state_scan",
 )
 
 _lock = threading.Lock()

@@ -8,9 +8,15 @@
 //            rows (32, or 64 for the tensor-core tiles; padded with -1), `tile_expert` names each tile's expert, `n_tiles` counts them.
 //   up       per tile: g = min(gate(h), limit), u = clamp(up(h), -limit, limit),
 //            a = g * sigmoid(1.702 g) * (u + 1), for the tile's rows gathered from h (expert kind 1);
-//            or, for experts without a gate, a = relu(up(h))^2 (expert kind 2).
+//            or, for experts without a gate, a = relu(up(h))^2 (expert kind 2); with limit 0 the gated kind
+//            has no clamps and the plain gate: a = silu(gate(h)) * up(h).
 //   down     per tile: the expert's down projection of a, filed at the pair's own place.
 //   combine  out[t] = sum_c weight[t][c] * down[t][c], summed in float in the order of the choices.
+//
+// A second router (route_all) scores by the softmax over ALL its outputs, chooses by score + correction among the
+// experts of the best groups, and may have more outputs than there are experts: a choice from `experts` on is
+// an identity expert, which has no weights.  align leaves such pairs out of the tiles and combine adds the
+// token's own row in their place.  combine also adds a shared expert's output times a gate per token.
 //
 // Products accumulate in float; gate and up are rounded to the working type before the activation, as
 // the projections of the dense feed-forward are.  A token's result depends on nothing but its own row
@@ -24,6 +30,18 @@
 #define MOE_BK 32
 #define MOE_MAX_EXPERTS 1024
 #define MOE_MAX_TOP 16
+
+// The gated expert's activation from its (rounded) gate and up products.  limit > 0: the clamped gate,
+// min(g, limit) * sigmoid(1.702 min(g, limit)) * (clamp(u, -limit, limit) + 1); limit == 0: no clamps and the
+// plain gate silu(g) * u.
+__device__ __forceinline__ float moe_gate(float g, float u, float limit) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+  }
+  return g / (1.f + expf(-g)) * u;
+}
 
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w, const float* __restrict__ b,
@@ -95,6 +113,113 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
   }
 }
 
+// The router of the softmax over all outputs (see sb_moe_route_all).  z holds outputs + 1 logits (the last one
+// the shared expert's gate, when asked for), then the scores, the choice numbers and the groups' maxima.
+template <typename T>
+__global__ void moe_route_all_kernel(const T* __restrict__ h, const float* __restrict__ w,
+                                     const float* __restrict__ correction, int* __restrict__ ids,
+                                     float* __restrict__ weights, float* __restrict__ gate_out, int width, int outputs,
+                                     int top, int groups, int keep, float weight_scale) {
+  extern __shared__ float z[];
+  float* score = z + outputs + 1;
+  float* choice = score + outputs;
+  float* best_of = choice + outputs;
+  pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
+  SB_BEHIND_WAIT(h);
+  const int row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const T* hr = h + (size_t)row * width;
+  const int rows = outputs + (gate_out ? 1 : 0);
+  const bool wide = width % 4 == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)hr % 8) == 0;
+  for (int e = warp; e < rows; e += warps) {
+    const float* wr = w + (size_t)e * width;
+    float a = 0.f;
+    if (wide && sizeof(T) == 2) {
+      const float4* w4 = reinterpret_cast<const float4*>(wr);
+      const uint2* h4 = reinterpret_cast<const uint2*>(hr);
+#pragma unroll 4
+      for (int c = lane; c < width / 4; c += 32) {
+        const float4 wv = w4[c];
+        const uint2 hv = h4[c];
+        a += __uint_as_float(hv.x << 16) * wv.x + __uint_as_float(hv.x & 0xffff0000u) * wv.y +
+             __uint_as_float(hv.y << 16) * wv.z + __uint_as_float(hv.y & 0xffff0000u) * wv.w;
+      }
+    } else {
+      for (int c = lane; c < width; c += 32) a += to_f<T>(hr[c]) * wr[c];
+    }
+    a = warp_sum(a);
+    if (lane == 0) z[e] = a;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  if (gate_out && lane == 0) gate_out[row] = 1.f / (1.f + expf(-z[outputs]));
+  float top_z = -INFINITY;
+  for (int e = lane; e < outputs; e += 32) top_z = fmaxf(top_z, z[e]);
+  top_z = warp_max(top_z);
+  float sum = 0.f;
+  for (int e = lane; e < outputs; e += 32) {
+    const float v = expf(z[e] - top_z);
+    score[e] = v;
+    sum += v;
+  }
+  sum = warp_sum(sum);
+  for (int e = lane; e < outputs; e += 32) {
+    score[e] /= sum;
+    choice[e] = score[e] + (correction ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  if (groups > 1) {
+    const int per = outputs / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float v = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) v = fmaxf(v, choice[e]);
+      best_of[g] = v;
+    }
+    __syncwarp();
+    // the `keep` best groups are marked with +inf, then every other group's outputs leave the choice
+    for (int c = 0; c < keep; ++c) {
+      float v = -INFINITY;
+      int at = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32)
+        if (best_of[g] != INFINITY && (best_of[g] > v || at == 0x7fffffff)) { v = best_of[g]; at = g; }
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (oa != 0x7fffffff && (at == 0x7fffffff || ov > v || (ov == v && oa < at))) { v = ov; at = oa; }
+      }
+      if (lane == 0 && at < groups) best_of[at] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < outputs; e += 32)
+      if (best_of[e / per] != INFINITY) choice[e] = -INFINITY;
+    __syncwarp();
+  }
+  float picked[MOE_MAX_TOP];
+  for (int c = 0; c < top; ++c) {
+    float v = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < outputs; e += 32)
+      if (choice[e] > v) { v = choice[e]; at = e; }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ov > v || (ov == v && oa < at)) { v = ov; at = oa; }
+    }
+    if (at >= outputs) at = 0;          // nothing left to choose from: keep the indices inside the table
+    picked[c] = score[at];
+    if (lane == 0) {
+      ids[(size_t)row * top + c] = at;
+      choice[at] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (lane == 0) {
+    float total = 0.f;
+    for (int c = 0; c < top; ++c) total += picked[c];
+    for (int c = 0; c < top; ++c) weights[(size_t)row * top + c] = picked[c] / (total + 1e-20f) * weight_scale;
+  }
+}
+
 // One block.  ids: [n_pairs]; sorted: [capacity] receives pair numbers or -1; tile_expert: [max_tiles].
 __global__ void moe_align_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __restrict__ sorted,
                                  int capacity, int* __restrict__ tile_expert, int* __restrict__ n_tiles, int bm) {
@@ -103,7 +228,9 @@ __global__ void moe_align_kernel(const int* __restrict__ ids, int n_pairs, int e
   SB_BEHIND_WAIT(ids);
   for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&count[ids[i]], 1);
+  // (an id from `experts` on names an identity expert: it has no tile)
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x)
+    if (ids[i] < experts) atomicAdd(&count[ids[i]], 1);
   __syncthreads();
   if (threadIdx.x == 0) {
     int off = 0, tiles = 0;
@@ -122,7 +249,7 @@ __global__ void moe_align_kernel(const int* __restrict__ ids, int n_pairs, int e
   __syncthreads();
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
     const int e = ids[i];
-    sorted[offset[e] + atomicAdd(&count[e], 1)] = i;
+    if (e < experts) sorted[offset[e] + atomicAdd(&count[e], 1)] = i;
   }
 }
 
@@ -205,10 +332,8 @@ moe_tile_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict_
       const int n = n0 + tx + 16 * j;
       if (n >= n_out) continue;
       if (MODE == 1) {
-        float g = rnd<T>(acc[0][i][j]), u = rnd<T>(acc[NW - 1][i][j]);
-        g = fminf(g, limit);
-        u = fminf(fmaxf(u, -limit), limit);
-        const float a = pair >= 0 ? g / (1.f + expf(-1.702f * g)) * (u + 1.f) : 0.f;
+        const float g = rnd<T>(acc[0][i][j]), u = rnd<T>(acc[NW - 1][i][j]);
+        const float a = pair >= 0 ? moe_gate(g, u, limit) : 0.f;
         y[((size_t)tile * MOE_BM + m) * n_out + n] = from_f<T>(a);
       } else if (MODE == 2) {
         const float u = fmaxf(rnd<T>(acc[0][i][j]), 0.f);
@@ -340,10 +465,8 @@ moe_tile_tc_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
     const int row_pair = src[m];
     if (n >= n_out) continue;
     if (MODE == 1) {
-      float g = rnd<bf16>(cs[(size_t)m * CLD + nn]), u = rnd<bf16>(cs[((size_t)(NW - 1) * MOE_TC_BM + m) * CLD + nn]);
-      g = fminf(g, limit);
-      u = fminf(fmaxf(u, -limit), limit);
-      const float a = row_pair >= 0 ? g / (1.f + expf(-1.702f * g)) * (u + 1.f) : 0.f;
+      const float g = rnd<bf16>(cs[(size_t)m * CLD + nn]), u = rnd<bf16>(cs[((size_t)(NW - 1) * MOE_TC_BM + m) * CLD + nn]);
+      const float a = row_pair >= 0 ? moe_gate(g, u, limit) : 0.f;
       y[((size_t)tile * MOE_TC_BM + m) * n_out + n] = from_f<bf16>(a);
     } else if (MODE == 2) {
       const float u = fmaxf(rnd<bf16>(cs[(size_t)m * CLD + nn]), 0.f);
@@ -495,12 +618,8 @@ moe_tile_big_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16
         if (MODE == 1) {
           float g0 = rnd<bf16>(acc[0][mb][nb][2 * h]), g1 = rnd<bf16>(acc[0][mb][nb][2 * h + 1]);
           float u0 = rnd<bf16>(acc[NW - 1][mb][nb][2 * h]), u1 = rnd<bf16>(acc[NW - 1][mb][nb][2 * h + 1]);
-          g0 = fminf(g0, limit);
-          g1 = fminf(g1, limit);
-          u0 = fminf(fmaxf(u0, -limit), limit);
-          u1 = fminf(fmaxf(u1, -limit), limit);
-          r0 = row_pair >= 0 ? g0 / (1.f + expf(-1.702f * g0)) * (u0 + 1.f) : 0.f;
-          r1 = row_pair >= 0 ? g1 / (1.f + expf(-1.702f * g1)) * (u1 + 1.f) : 0.f;
+          r0 = row_pair >= 0 ? moe_gate(g0, u0, limit) : 0.f;
+          r1 = row_pair >= 0 ? moe_gate(g1, u1, limit) : 0.f;
         } else if (MODE == 2) {
           const float u0 = fmaxf(rnd<bf16>(acc[0][mb][nb][2 * h]), 0.f), u1 = fmaxf(rnd<bf16>(acc[0][mb][nb][2 * h + 1]), 0.f);
           r0 = row_pair >= 0 ? u0 * u0 : 0.f;
@@ -629,9 +748,7 @@ moe_few_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __r
   const int n = n_first + lane / MOE_FEW, r = lane % MOE_FEW;
   if (n < n_out && r < nr) {
     if (MODE == 1) {
-      const float g = fminf(rnd<bf16>(v0), limit);
-      const float u = fminf(fmaxf(rnd<bf16>(v1), -limit), limit);
-      y[((size_t)tile * MOE_FEW + r) * n_out + n] = from_f<bf16>(g / (1.f + expf(-1.702f * g)) * (u + 1.f));
+      y[((size_t)tile * MOE_FEW + r) * n_out + n] = from_f<bf16>(moe_gate(rnd<bf16>(v0), rnd<bf16>(v1), limit));
     } else if (MODE == 2) {
       const float u = fmaxf(rnd<bf16>(v0), 0.f);
       y[((size_t)tile * MOE_FEW + r) * n_out + n] = from_f<bf16>(u * u);
@@ -658,17 +775,29 @@ __global__ void moe_gather_kernel(const bf16* __restrict__ h, const int* __restr
   for (int c = threadIdx.x; c < width / 8; c += blockDim.x) to[c] = pair >= 0 ? from[c] : make_uint4(0u, 0u, 0u, 0u);
 }
 
+// ids / h (null: every choice is a real expert): a choice from `experts` on stands for the token's own row h[t].
+// shared / shared_gate (null: none): shared_gate[t] * shared[t] is added.
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ down, const float* __restrict__ weights, T* __restrict__ out,
-                                   int width, int top) {
+                                   int width, int top, const int* __restrict__ ids, int experts, const T* __restrict__ h,
+                                   const T* __restrict__ shared, const float* __restrict__ shared_gate) {
   pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(down);
   SB_BEHIND_WAIT(weights);
+  SB_BEHIND_WAIT(ids);
+  SB_BEHIND_WAIT(h);
+  SB_BEHIND_WAIT(shared);
+  SB_BEHIND_WAIT(shared_gate);
   const int row = blockIdx.x;
+  const float sg = shared ? shared_gate[row] : 0.f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float a = 0.f;
-    for (int j = 0; j < top; ++j)
-      a += weights[(size_t)row * top + j] * to_f<T>(down[((size_t)row * top + j) * width + c]);
+    for (int j = 0; j < top; ++j) {
+      const bool own = ids && ids[(size_t)row * top + j] >= experts;
+      a += weights[(size_t)row * top + j] *
+           to_f<T>(own ? h[(size_t)row * width + c] : down[((size_t)row * top + j) * width + c]);
+    }
+    if (shared) a += sg * to_f<T>(shared[(size_t)row * width + c]);
     out[(size_t)row * width + c] = from_f<T>(a);
   }
 }
@@ -788,14 +917,37 @@ int sb_moe_tiles(int dtype, int up, int tile_rows, const void* x, const void* w,
 }
 
 int sb_moe_combine(int dtype, const void* down, const float* weights, void* out, int n_tokens, int width, int top,
+                   const int* ids, int experts, const void* h, const void* shared, const float* shared_gate,
                    cudaStream_t s) {
   if (n_tokens == 0) return 0;
+  if ((ids != nullptr) != (h != nullptr) || (shared != nullptr) != (shared_gate != nullptr)) return -2;
   const int threads = width >= 1024 ? 256 : 128;
   if (dtype == 0)
     return launch_dependent(moe_combine_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)down,
-                            weights, (float*)out, width, top);
+                            weights, (float*)out, width, top, ids, experts, (const float*)h, (const float*)shared,
+                            shared_gate);
   return launch_dependent(moe_combine_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, (const bf16*)down, weights,
-                          (bf16*)out, width, top);
+                          (bf16*)out, width, top, ids, experts, (const bf16*)h, (const bf16*)shared, shared_gate);
+}
+
+// The router that scores by the softmax over all `outputs` rows of w (float [outputs (+ 1), width]): the choice
+// goes by score + correction (float [outputs] or null) among the outputs of the `keep` of `groups` equal groups
+// of neighbours whose largest such number is largest (the lower index first among equals, here and in the
+// choice); weights: the chosen plain scores over their sum (+ 1e-20), times weight_scale.  gate_out (null:
+// none): w has one row more, and gate_out[t] = sigmoid of that row's product.
+int sb_moe_route_all(int dtype, const void* h, const float* w, const float* correction, int* ids, float* weights,
+                     float* gate_out, int n_tokens, int width, int outputs, int top, int groups, int keep,
+                     float weight_scale, cudaStream_t s) {
+  if (n_tokens == 0) return 0;
+  if (outputs < 1 || outputs > MOE_MAX_EXPERTS || top < 1 || top > MOE_MAX_TOP) return -2;
+  if (groups < 1 || outputs % groups || keep < 1 || keep > groups || top > outputs / groups * keep) return -2;
+  const size_t smem = (size_t)(3 * outputs + 1 + groups) * sizeof(float);
+  const int threads = n_tokens <= 64 ? (outputs >= 16 ? 512 : outputs > 4 ? 256 : 128) : 128;
+  if (dtype == 0)
+    return launch_dependent(moe_route_all_kernel<float>, dim3(n_tokens), dim3(threads), smem, s, (const float*)h, w,
+                            correction, ids, weights, gate_out, width, outputs, top, groups, keep, weight_scale);
+  return launch_dependent(moe_route_all_kernel<bf16>, dim3(n_tokens), dim3(threads), smem, s, (const bf16*)h, w,
+                          correction, ids, weights, gate_out, width, outputs, top, groups, keep, weight_scale);
 }
 
 }  // extern "C"

@@ -1607,9 +1607,9 @@ def moe_limits():
 
 
 #: how the chosen experts' weights are formed from their logits, and the code the router takes
-MOE_SCORINGS = {"softmax_top": 0, "sigmoid_normalised": 1}
-#: the experts the tile kernels know, and the code of their up pass
-MOE_EXPERTS = {"gated_clamped": 1, "relu2": 2}
+MOE_SCORINGS = {"softmax_top": 0, "sigmoid_normalised": 1, "softmax_all": 2}
+#: the experts the tile kernels know, and the code of their up pass (``gated_silu`` is the gated pass without clamps)
+MOE_EXPERTS = {"gated_clamped": 1, "relu2": 2, "gated_silu": 1}
 
 
 def moe_route(h, router, router_bias, top, scoring="softmax_top", weight_scale=1.0):
@@ -1635,7 +1635,33 @@ def moe_route(h, router, router_bias, top, scoring="softmax_top", weight_scale=1
     return ids, weights
 
 
-def moe_experts(h, ids, weights, gate_up, down, limit=0.0, expert="gated_clamped", tile_rows=None, status=None):
+def moe_route_all(h, router, correction, top, groups=1, keep=1, weight_scale=1.0, shared_gate=False):
+    """The router that scores by the softmax over ALL rows of ``router`` (float32 ``[N, W]``): ``(ids int32 [T, top],
+    weights float32 [T, top])``, the ``top`` largest of ``score + correction`` (float32 ``[N]`` or None) among the
+    outputs of the ``keep`` of ``groups`` equal groups of neighbours whose largest such number is largest (the lower
+    index first among equals), weighted by their plain scores over their sum (+ 1e-20) times ``weight_scale``.  With
+    ``shared_gate`` the router has one row more and a third result, float32 ``[T]``: the sigmoid of that row's
+    product (the gate of a shared expert)."""
+    _need(h, "h", None, 2)
+    outputs = router.shape[0] - (1 if shared_gate else 0)
+    _f32(router, "router", (router.shape[0], h.shape[1]))
+    if correction is not None:
+        _f32(correction, "correction", (outputs,))
+    ids = torch.empty((h.shape[0], top), dtype=torch.int32, device=h.device)
+    weights = torch.empty((h.shape[0], top), dtype=torch.float32, device=h.device)
+    gate = torch.empty((h.shape[0],), dtype=torch.float32, device=h.device) if shared_gate else None
+    rc = _lib("moe").sb_moe_route_all(_code(h.dtype), _ptr(h), _ptr(router), _ptr(correction), _ptr(ids), _ptr(weights),
+                                      _ptr(gate), h.shape[0], h.shape[1], outputs, top, groups, keep,
+                                      ctypes.c_float(weight_scale), _stream())
+    if rc == -2:
+        raise KernelError(f"the router takes up to {moe_limits()[0]} outputs and {moe_limits()[1]} choices among the "
+                          f"kept groups, not {outputs} outputs, {top} choices, {keep} of {groups} groups")
+    _check(rc, "moe_route_all")
+    return (ids, weights, gate) if shared_gate else (ids, weights)
+
+
+def moe_experts(h, ids, weights, gate_up, down, limit=0.0, expert="gated_clamped", tile_rows=None, status=None,
+                identity=False, shared=None, shared_gate=None):
     """The chosen experts of every row and their weighted sum: ``gate_up`` ``[E, 2 * F, W]`` (an expert's
     gate rows, then its up rows), ``down`` ``[E, W, F]``; an expert is ``down(g * sigmoid(1.702 g) * (u +
     1))`` with ``g = min(gate(h), limit)`` and ``u = clamp(up(h), -limit, limit)``.  With ``expert``
@@ -1643,11 +1669,26 @@ def moe_experts(h, ids, weights, gate_up, down, limit=0.0, expert="gated_clamped
     ``down(relu(up(h))^2)``.  Returns ``[T, W]``.  ``tile_rows`` names the tile kind (32: plain; 4: the few-row kernel;
     64 and 128: ``mma.sync`` tiles; 256: the grouped tcgen05 product over rows gathered in the experts' order) instead of
     the one the step's shape chooses: 4 up to four rows an expert on average, 128 from 128, 256 from 256.  ``status``: the
-    device word a tcgen05 wait that ran out is noted in."""
+    device word a tcgen05 wait that ran out is noted in.
+
+    ``expert`` ``"gated_silu"``: ``down(silu(gate(h)) * up(h))``, no clamps.  ``identity``: an id from ``E`` on names
+    an expert without weights that hands the row itself on.  ``shared`` ``[T, W]`` with ``shared_gate`` float32
+    ``[T]``: ``shared_gate[t] * shared[t]`` is added to row ``t`` of the result."""
     if expert not in MOE_EXPERTS:
         raise KernelError(f"no expert kind {expert!r} (known: {', '.join(MOE_EXPERTS)})")
     up_mode = MOE_EXPERTS[expert]
+    if expert == "gated_silu":
+        limit = 0.0                       # the gated pass without clamps
+    elif up_mode == 1 and not limit > 0.0:
+        raise KernelError(f"the clamped gate needs a positive limit, not {limit}")
     _need(h, "h", None, 2)
+    if shared is not None:
+        _need(shared, "shared", h.dtype, 2)
+        _f32(shared_gate, "shared gate", (h.shape[0],))
+        if tuple(shared.shape) != tuple(h.shape):
+            raise KernelError(f"the shared expert's output {tuple(shared.shape)} does not match the rows {tuple(h.shape)}")
+    extras = (_ptr(ids if identity else None), gate_up.shape[0], _ptr(h if identity else None), _ptr(shared),
+              _ptr(shared_gate if shared is not None else None))
     _need(gate_up, "gate_up", h.dtype, 3)
     _need(down, "down", h.dtype, 3)
     _need(ids, "ids", torch.int32, 2)
@@ -1681,14 +1722,16 @@ def moe_experts(h, ids, weights, gate_up, down, limit=0.0, expert="gated_clamped
         rc = lib.sb_moe_gather(_ptr(h), _ptr(sorted_pairs), _ptr(n_tiles), bm, top, _ptr(gathered), capacity, width, _stream())
         _check(rc, "moe_gather")
         rc = grouped(_ptr(gathered), _ptr(gate_up), _ptr(act), capacity, inner, width, experts, _ptr(tile_expert),
-                     _ptr(n_tiles), max_tiles, None, GATE_CLAMPED if up_mode == 1 else 0, 1 if up_mode == 2 else 0,
+                     _ptr(n_tiles), max_tiles, None,
+                     (GATE_CLAMPED if limit > 0.0 else ACTIVATIONS["silu"]) if up_mode == 1 else 0, 1 if up_mode == 2 else 0,
                      ctypes.c_float(limit), _ptr(status), _stream())
         _check(rc, "moe_up (grouped tcgen05)")
         rc = grouped(_ptr(act), _ptr(down), _ptr(per_pair), capacity, width, inner, experts, _ptr(tile_expert),
                      _ptr(n_tiles), max_tiles, _ptr(sorted_pairs), 0, 0, ctypes.c_float(0.0), _ptr(status), _stream())
         _check(rc, "moe_down (grouped tcgen05)")
         out = torch.empty_like(h)
-        rc = lib.sb_moe_combine(_code(h.dtype), _ptr(per_pair), _ptr(weights), _ptr(out), n_tokens, width, top, _stream())
+        rc = lib.sb_moe_combine(_code(h.dtype), _ptr(per_pair), _ptr(weights), _ptr(out), n_tokens, width, top, *extras,
+                                _stream())
         _check(rc, "moe_combine")
         return out
     rc = lib.sb_moe_tiles(_code(h.dtype), up_mode, bm, _ptr(h), _ptr(gate_up), _ptr(act), _ptr(sorted_pairs), _ptr(tile_expert),
@@ -1698,7 +1741,8 @@ def moe_experts(h, ids, weights, gate_up, down, limit=0.0, expert="gated_clamped
                           _ptr(tile_expert), _ptr(n_tiles), max_tiles, inner, width, top, ctypes.c_float(limit), _stream())
     _check(rc, "moe_down")
     out = torch.empty_like(h)
-    rc = lib.sb_moe_combine(_code(h.dtype), _ptr(per_pair), _ptr(weights), _ptr(out), n_tokens, width, top, _stream())
+    rc = lib.sb_moe_combine(_code(h.dtype), _ptr(per_pair), _ptr(weights), _ptr(out), n_tokens, width, top, *extras,
+                                _stream())
     _check(rc, "moe_combine")
     return out
 
@@ -1812,6 +1856,54 @@ def sink_prepare(proj, heads, kv_heads, dim, vdim, tok_pos, tok_slot, block_tabl
         _ptr(gate), n_tokens, heads, kv_heads, dim, vdim, int(write_cache), _stream())
     _check(rc, "sink_prepare")
     return gate
+
+
+def sink_tables(rotation, dim: int):
+    """``(cos, sin, dims)`` for ``sink_prepare_rot``: it turns the first ``dims`` entries of a head, entry ``2i``
+    with ``2i + 1``; None: nothing turns."""
+    if rotation is None:
+        return None, None, 0
+    if rotation.layout != "interleaved" or rotation.rotary_dim > dim or rotation.rotary_dim % 2:
+        raise KernelError(f"this attention turns up to {dim} leading entries of a head in interleaved layout; asked for "
+                          f"{rotation.rotary_dim} in {rotation.layout!r} layout")
+    return rotation.cos, rotation.sin, rotation.rotary_dim
+
+
+def sink_prepare_rot(proj, heads, kv_heads, dim, vdim, tok_pos, tok_slot, block_table, k_store, v_store, cos_table,
+                     sin_table, rot_dims, values_from_keys=False, write_cache=True):
+    """``sink_prepare`` for a layer with rotary positions and no gates: ``proj`` = ``[q | k | v]`` (``[q | k]`` with
+    ``values_from_keys``, ``[q]`` with ``write_cache`` false; up to 7 unused entries may follow).  The first
+    ``rot_dims`` entries of every query and key head turn by the token's position, entry ``2i`` with ``2i + 1``
+    (float32 tables ``[positions, rot_dims / 2]``): the queries in place, the keys on their way into the cache.
+    Values are filed as they are; with ``values_from_keys`` a head's value is its key before the turn."""
+    _need(proj, "proj", None, 2)
+    n_tokens = proj.shape[0]
+    want = heads * dim + (kv_heads * (dim + (0 if values_from_keys else vdim)) if write_cache else 0)
+    if not want <= proj.shape[1] < want + 8:
+        raise KernelError(f"proj has width {proj.shape[1]}, expected {want} (and up to 7 entries of padding)")
+    _need(tok_pos, "tok_pos", torch.int32, 1)
+    _need(tok_slot, "tok_slot", torch.int32, 1)
+    _need(block_table, "block_table", torch.int32, 2)
+    if rot_dims:
+        _need(cos_table, "cos table", torch.float32, 2)
+        _need(sin_table, "sin table", torch.float32, 2)
+        if cos_table.shape[1] != rot_dims // 2 or tuple(sin_table.shape) != tuple(cos_table.shape):
+            raise KernelError(f"rotation tables {tuple(cos_table.shape)} do not turn {rot_dims} entries")
+    if write_cache:
+        _need(k_store, "key pages", proj.dtype, 4)
+        _need(v_store, "value pages", proj.dtype, 4)
+        if tuple(k_store.shape[1:]) != (kv_heads, PAGE_TOKENS, dim) or tuple(v_store.shape[1:]) != (kv_heads, PAGE_TOKENS, vdim):
+            raise KernelError(f"cache pages have shapes {tuple(k_store.shape)} / {tuple(v_store.shape)}, expected "
+                              f"[pages, {kv_heads}, {PAGE_TOKENS}, {dim}] / [.., {vdim}]")
+    rc = _lib("attention_sink").sb_sink_prepare_rot(
+        _code(proj.dtype), _ptr(proj), proj.shape[1], _ptr(tok_pos), _ptr(tok_slot), _ptr(block_table),
+        block_table.shape[1], _ptr(k_store if write_cache else None), _ptr(v_store if write_cache else None),
+        _ptr(cos_table if rot_dims else None), _ptr(sin_table if rot_dims else None), int(rot_dims), n_tokens, heads,
+        kv_heads, dim, vdim, int(values_from_keys), int(write_cache), _stream())
+    if rc == -2:
+        raise KernelError(f"sink_prepare_rot: rot_dims={rot_dims} must be even and at most dim={dim}; values taken from "
+                          f"keys need vdim == dim (got {vdim})")
+    _check(rc, "sink_prepare_rot")
 
 
 def _sink_check(q, k_store, v_store, heads, kv_heads, dim, vdim, penalty, sink, gate):
@@ -1993,3 +2085,182 @@ def linear_gated_clamped(x, weight, limit, status=None):
         _check(rc, "gemm_prompt_tcgen05 (clamped gate)")
         return out
     return gated_clamped(linear(x, weight, status=status), limit)
+
+
+# ---------------------------------------------------------------------------------------- per-channel recurrences
+
+def _at(t, offset: int):
+    """The address of element ``offset`` of a contiguous tensor."""
+    return ctypes.c_void_p(t.data_ptr() + offset * t.element_size())
+
+
+def _seq_arrays(seq_slot, seq_q_start, seq_q_len):
+    for name, t in (("seq_slot", seq_slot), ("seq_q_start", seq_q_start), ("seq_q_len", seq_q_len)):
+        _need(t, name, torch.int32, 1)
+    return seq_slot.shape[0]
+
+
+def conv_max_taps() -> int:
+    return _lib("short_conv").sb_conv_max_taps()
+
+
+def short_conv(x, col, channels, taps, bias, in_bias, state, state_at, seq_slot, seq_q_start, seq_q_len, max_q_len,
+               activation=None):
+    """A causal convolution over time with one filter per channel, over the sequences of a step:
+    ``y[t, c] = act(bias[c] + sum_j taps[c, K - 1 - j] * (x[t - j, col + c] + in_bias[c]))``, zeros in front of a
+    sequence.  ``x`` ``[T, N]`` (the channels are its columns ``col .. col + channels``); ``taps`` float32
+    ``[channels, K]``; ``bias``, ``in_bias`` float32 ``[channels]`` or None; ``activation`` None or ``"silu"``.
+    ``state`` float32 ``[slots, M]``: a slot's last ``K - 1`` inputs (``(K - 1) * channels`` floats from
+    ``state_at`` on) stand in front of the tokens it brings and are replaced by the step's last ones.
+    ``max_q_len``: the most tokens a sequence brings.  Returns ``[T, channels]`` in the type of ``x``."""
+    _need(x, "x", None, 2)
+    _need(taps, "taps", torch.float32, 2)
+    k = taps.shape[1]
+    if taps.shape[0] != channels:
+        raise KernelError(f"taps {tuple(taps.shape)} do not filter {channels} channels")
+    if bias is not None:
+        _f32(bias, "bias", (channels,))
+    if in_bias is not None:
+        _f32(in_bias, "in_bias", (channels,))
+    _need(state, "state", torch.float32, 2)
+    if col < 0 or col + channels > x.shape[1] or state_at < 0 or state_at + (k - 1) * channels > state.shape[1]:
+        raise KernelError(f"{channels} channels from column {col} of rows of {x.shape[1]}, or {k - 1} rows of them from "
+                          f"float {state_at} of a slot's {state.shape[1]}, do not fit")
+    if activation not in (None, "silu"):
+        raise KernelError(f"the short convolution applies silu or nothing, not {activation!r}")
+    n_seqs = _seq_arrays(seq_slot, seq_q_start, seq_q_len)
+    y = torch.empty((x.shape[0], channels), dtype=x.dtype, device=x.device)
+    rc = _lib("short_conv").sb_short_conv(
+        _code(x.dtype), _at(x, col), x.shape[1], _ptr(taps), _ptr(bias), _ptr(in_bias), _ptr(y), channels,
+        _at(state, state_at), ctypes.c_longlong(state.shape[1]), _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len),
+        n_seqs, int(max_q_len), channels, k, 1 if activation == "silu" else 0, _stream())
+    if rc == -2:
+        raise KernelError(f"the short convolution takes 1 to {conv_max_taps()} taps, not {k}")
+    _check(rc, "short_conv")
+    return y
+
+
+def glru_scan(u, gates, r_bias, i_bias, lam, decay_scale, proj, y_col, y_bias, state, state_at, seq_slot, seq_q_start,
+              seq_q_len, max_q_len):
+    """The real-gated linear recurrent unit over the sequences of a step, per channel ``c`` of ``C``:
+    ``r = sigmoid(zr + r_bias)``, ``i = sigmoid(zi + i_bias)``, ``a = exp(-decay_scale * r * softplus(lam))``,
+    ``S <- a S + sqrt(1 - a^2) i u`` and the result ``S * gelu_tanh(y + y_bias)``.  ``u`` ``[T, C]``; ``gates`` float32
+    ``[blocks, T, 2 * C / blocks]``: for each block of channels its ``zr`` then its ``zi``; ``y`` = columns ``y_col ..
+    y_col + C`` of ``proj`` ``[T, N]``; the biases and ``lam`` float32 ``[C]`` (``y_bias`` may be None).  ``state``
+    float32 ``[slots, M]``: a slot's ``S`` is its ``C`` floats from ``state_at`` on.  Returns ``[T, C]``."""
+    _need(u, "u", None, 2)
+    n_tokens, channels = u.shape
+    _need(gates, "gates", torch.float32, 3)
+    blocks = gates.shape[0]
+    if blocks < 1 or channels % blocks or tuple(gates.shape) != (blocks, n_tokens, 2 * channels // blocks):
+        raise KernelError(f"gate logits {tuple(gates.shape)} do not fit {n_tokens} tokens of {channels} channels")
+    for name, t in (("r_bias", r_bias), ("i_bias", i_bias), ("lam", lam)):
+        _f32(t, name, (channels,))
+    if y_bias is not None:
+        _f32(y_bias, "y_bias", (channels,))
+    _need(proj, "proj", u.dtype, 2)
+    _need(state, "state", torch.float32, 2)
+    if proj.shape[0] != n_tokens or y_col < 0 or y_col + channels > proj.shape[1] or state_at + channels > state.shape[1]:
+        raise KernelError("the gated branch or the state does not hold the channels asked for")
+    n_seqs = _seq_arrays(seq_slot, seq_q_start, seq_q_len)
+    out = torch.empty_like(u)
+    rc = _lib("short_conv").sb_glru_scan(
+        _code(u.dtype), _ptr(u), channels, _ptr(gates), n_tokens, channels // blocks, _ptr(r_bias), _ptr(i_bias), _ptr(lam),
+        ctypes.c_float(decay_scale), _at(proj, y_col), proj.shape[1], _ptr(y_bias), _ptr(out), _at(state, state_at),
+        ctypes.c_longlong(state.shape[1]), _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), n_seqs, int(max_q_len),
+        channels, _stream())
+    _check(rc, "glru_scan")
+    return out
+
+
+# ---------------------------------------------------------------------------------------- recurrences with a matrix state
+
+SCAN_MODES = {"state_space": 0, "gated_delta": 1}
+
+
+def scan_max_state() -> int:
+    return _lib("state_scan").sb_scan_max_state()
+
+
+def state_scan(mode, q, k, v, a_raw, b_raw, A_log, dt_bias, skip, state, state_at, seq_slot, seq_q_start, seq_q_len,
+               heads, groups, n_state, v_dim):
+    """A linear recurrence with a state ``S`` ``[n_state, v_dim]`` per head over the sequences of a step.
+
+    ``q, k, v, a_raw, b_raw`` are ``(tensor [T, N], first column)`` pairs of the working type: ``groups`` heads of
+    ``n_state`` queries and keys (head ``h`` reads ``h // (heads // groups)``), ``heads`` heads of ``v_dim`` values,
+    ``heads`` entries each of ``a_raw`` and ``b_raw``.  ``A_log``, ``dt_bias`` (and ``skip`` or None) float32 ``[heads]``.
+
+    ``"state_space"``: ``dt = softplus(a_raw + dt_bias)``, ``S <- exp(-exp(A_log) dt) S + k (dt v)^T``, ``o = S^T q +
+    skip * v`` (``b_raw`` None).  ``"gated_delta"``: q and k made unit vectors (``x / sqrt(sum x^2 + 1e-6)``), q times
+    ``n_state ** -0.5``; ``S <- exp(-exp(A_log) softplus(a_raw + dt_bias)) S``, ``u = sigmoid(b_raw) (v - S^T k)``, ``S
+    <- S + k u^T``, ``o = S^T q``.  ``state`` float32 ``[slots, M]``: a slot's ``[heads, n_state, v_dim]`` from
+    ``state_at`` on, read at the start and written at the end.  Returns float32 ``[T, heads * v_dim]``."""
+    if mode not in SCAN_MODES:
+        raise KernelError(f"no recurrence {mode!r} (known: {', '.join(SCAN_MODES)})")
+    dtype = q[0].dtype
+    n_tokens = q[0].shape[0]
+    args = []
+    for name, pair, width in (("q", q, groups * n_state), ("k", k, groups * n_state), ("v", v, heads * v_dim),
+                              ("a_raw", a_raw, heads), ("b_raw", b_raw, heads)):
+        if pair is None:
+            args += [ctypes.c_void_p(0), 0]
+            continue
+        t, col = pair
+        _need(t, name, dtype, 2)
+        if t.shape[0] != n_tokens or col < 0 or col + width > t.shape[1]:
+            raise KernelError(f"{name}: {width} columns from {col} of {tuple(t.shape)} do not fit {n_tokens} tokens")
+        args += [_at(t, col), t.shape[1]]
+    _f32(A_log, "A_log", (heads,))
+    _f32(dt_bias, "dt_bias", (heads,))
+    if skip is not None:
+        _f32(skip, "skip", (heads,))
+    _need(state, "state", torch.float32, 2)
+    if state_at < 0 or state_at + heads * n_state * v_dim > state.shape[1]:
+        raise KernelError(f"a slot's {state.shape[1]} floats do not hold {heads} states of {n_state} x {v_dim} from {state_at}")
+    n_seqs = _seq_arrays(seq_slot, seq_q_start, seq_q_len)
+    out = torch.empty((n_tokens, heads * v_dim), dtype=torch.float32, device=state.device)
+    rc = _lib("state_scan").sb_state_scan(
+        _code(dtype), SCAN_MODES[mode], *args, _ptr(A_log), _ptr(dt_bias), _ptr(skip), _at(state, state_at),
+        ctypes.c_longlong(state.shape[1]), _ptr(out), _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), n_seqs, heads,
+        groups, n_state, v_dim, _stream())
+    if rc == -2:
+        raise KernelError(f"the recurrence takes states of 1 to {scan_max_state()} rows and heads in whole groups, not "
+                          f"{n_state} rows, {heads} heads, {groups} groups")
+    _check(rc, "state_scan")
+    return out
+
+
+def group_norm_gate(o, z, z_col, weight, parts, eps, gate_first, dtype):
+    """The RMS norm of each of the ``parts`` equal parts of a float32 row ``o`` ``[T, N]`` with ``silu`` of the
+    gate ``z`` (columns ``z_col .. z_col + N`` of a ``[T, M]`` tensor of ``dtype``): ``gate_first``: ``rms(o *
+    silu(z)) * w``; else ``rms(o) * w * silu(z)``.  ``weight`` float32 of ``N`` entries, or of one part's size when
+    the parts share it.  Returns ``[T, N]`` in ``dtype``."""
+    _need(o, "o", torch.float32, 2)
+    n_tokens, width = o.shape
+    _need(z, "z", dtype, 2)
+    _need(weight, "weight", torch.float32, 1)
+    if parts < 1 or width % parts or z.shape[0] != n_tokens or z_col < 0 or z_col + width > z.shape[1]:
+        raise KernelError(f"rows of {width} in {parts} parts with a gate from column {z_col} of {tuple(z.shape)} do not fit")
+    if weight.shape[0] not in (width, width // parts):
+        raise KernelError(f"a gain of {weight.shape[0]} entries fits neither the row ({width}) nor a part ({width // parts})")
+    y = torch.empty((n_tokens, width), dtype=dtype, device=o.device)
+    rc = _lib("state_scan").sb_group_norm_gate(_code(dtype), _ptr(o), _at(z, z_col), z.shape[1], _ptr(weight),
+                                               weight.shape[0], _ptr(y), n_tokens, parts, width // parts,
+                                               ctypes.c_float(eps), 0 if gate_first else 1, _stream())
+    _check(rc, "group_norm_gate")
+    return y
+
+
+def norm_pair_mean(a, b, gain_a, gain_b, eps):
+    """``(rms(a) * gain_a + rms(b) * gain_b) / 2`` row by row for ``a``, ``b`` ``[T, W]`` and float32 gains ``[W]``."""
+    _need(a, "a", None, 2)
+    _need(b, "b", a.dtype, 2)
+    if tuple(a.shape) != tuple(b.shape):
+        raise KernelError(f"rows {tuple(a.shape)} and {tuple(b.shape)} differ")
+    _f32(gain_a, "gain_a", (a.shape[1],))
+    _f32(gain_b, "gain_b", (a.shape[1],))
+    out = torch.empty_like(a)
+    rc = _lib("state_scan").sb_norm_pair_mean(_code(a.dtype), _ptr(a), _ptr(b), _ptr(gain_a), _ptr(gain_b), _ptr(out),
+                                              a.shape[0], a.shape[1], ctypes.c_float(eps), _stream())
+    _check(rc, "norm_pair_mean")
+    return out

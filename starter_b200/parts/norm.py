@@ -13,6 +13,8 @@ class RMSNorm(Part):
     def param_specs(self):
         if getattr(self.spec, "unit_offset", False):
             return {"weight": ParamSpec((self.spec.size,), "gain_offset")}
+        if getattr(self.spec, "gain_32bit", False):
+            return {"weight": ParamSpec((self.spec.size,), "gain32")}
         return {"weight": ParamSpec((self.spec.size,), "gain")}
 
     def set_params(self, params):

@@ -27,11 +27,13 @@ from .attention import GroupedQueryAttention
 from .attention_diff import DifferentialAttention
 from .attention_latent import LatentAttention
 from .attention_sink import SinkAttention
-from .block import PreNormBlock
+from .block import PreNorm32Block, PreNorm32MixerOnlyBlock, PreNormBlock
 from .depth import DepthAverage, DepthMixerOnlyBlock, DepthPreNormBlock
 from .feedforward import BiasedFeedForward, ClampedGatedFeedForward, GatedFeedForward, RoutedExperts
 from .hyper import HyperConnection, HyperMixerOnlyBlock, HyperPreNormBlock
 from .norm import RMSNorm
+from .parallel import ParallelMixer
+from .recurrent import GatedDeltaMixer, GatedLinearRecurrence, StateSpaceMixer
 from .norm_dyt import DynamicTanh
 from .norm_layer import LayerNorm
 from .rotary import InterleavedRotaryTable, PartialRotaryTable, RotaryTable
@@ -80,3 +82,9 @@ register("position", "rope_partial", PartialRotaryTable)
 register("connection", "depth_average", DepthAverage)
 register("arrangement", "depth_prenorm", DepthPreNormBlock)
 register("arrangement", "depth_mixer_only", DepthMixerOnlyBlock)
+register("arrangement", "prenorm32", PreNorm32Block)
+register("arrangement", "prenorm32_mixer_only", PreNorm32MixerOnlyBlock)
+register("mixer", "gated_linear_recurrence", GatedLinearRecurrence)
+register("mixer", "state_space", StateSpaceMixer)
+register("mixer", "gated_delta", GatedDeltaMixer)
+register("mixer", "parallel", ParallelMixer)
