@@ -134,9 +134,10 @@ def left_mixer(h, w, p, m, positions):
     q = (h @ w[p + "q"].T).reshape(T, m["heads"], m["dim"])
     k = (h @ w[p + "k"].T).reshape(T, m["kv_heads"], m["dim"])
     v = k
-    q = rotate_pairs(q, positions, m["rot"]["base"], m["rot"]["dims"])
-    k = rotate_pairs(k, positions, m["rot"]["base"], m["rot"]["dims"])
-    a = window_attention(q, k, v, m["scale"], m["mask"]["size"])
+    if m.get("rot") is not None:
+        q = rotate_pairs(q, positions, m["rot"]["base"], m["rot"]["dims"])
+        k = rotate_pairs(k, positions, m["rot"]["base"], m["rot"]["dims"])
+    a = window_attention(q, k, v, m["scale"], m["mask"]["size"] if m.get("mask") is not None else T)
     return a.reshape(T, -1) @ w[p + "o"].T
 
 
