@@ -735,6 +735,174 @@ def korurax_kernels_alone(ops, out, name, rows, x, blocks, spec, cache, ctx, siz
         out[f"{name}: experts (up, down, sum)"] = bw(us, used * 2 * fs.intermediate_size * w * 2)
 
 
+def bavedra_config(size: dict, layers: int) -> dict:
+    """Bavedra at ``size``: of every four layers a delta-rule one with a dense feed-forward, a recurrent unit with
+    routed experts, window attention beside a state-space recurrence with routed experts, and a delta-rule one with
+    routed experts.  Delta heads of 128 x 128 (half as many query/key heads), a recurrent unit as wide as the model in
+    blocks of 256, attention heads of 128 with a window of 1,024 and half of each head rotated, state-space heads of 64
+    with a state of 128; 16 experts of a quarter of the dense width and four identity experts in four groups of which
+    two are kept, four a token, a shared expert of the same size (about as many active feed-forward rows as the dense
+    layer)."""
+    w, out = size["width"], []
+    inner = size["ff"] // 4 // 64 * 64
+    moe = dict(kind="moe", expert=dict(ff=inner), shared=dict(ff=inner),
+               router=dict(experts=16, top=4, identity=4, groups=dict(count=4, keep=2)))
+    dense = dict(kind="dense", ff=size["ff"])
+    delta = dict(heads=w // 128, kv_heads=max(1, w // 256), dim=128, vdim=128, conv=4)
+    for i in range(layers):
+        if i % 4 in (0, 3):
+            mixer, kind = delta, "delta"
+        elif i % 4 == 1:
+            mixer, kind = dict(width=w, blocks=w // 256, conv=4), "rglru"
+        else:
+            mixer, kind = dict(left=dict(heads=size["heads"], kv_heads=size["kv_heads"], dim=128, vdim=128, scale=128 ** -0.5,
+                                         mask=dict(size=1024), rot=dict(base=1e6, dims=64)),
+                               right=dict(heads=w // 64, vdim=64, state=128, groups=1, conv=4, norm_groups=1)), "parallel"
+        out.append(dict(type=kind, mixer=mixer, mlp=dense if i % 4 == 0 else moe))
+    return dict(architecture="Bavedra", vocab=size["vocab"], width=w, embedding=dict(scale=16.0), norm=dict(eps=1e-6),
+                layers=out)
+
+
+def bavedra_kernels_alone(ops, out, name, rows, x, blocks, spec, cache, ctx, size, batch, context, prompt_len, rnd,
+                          in_graph, bw, tc):
+    """Bavedra's own kernels alone at ``rows`` rows, once per layer inside a CUDA graph."""
+    import torch
+
+    w, dev, bf = size["width"], x.device, x.dtype
+    res = torch.randn(rows, w, device=dev)
+    us = in_graph([lambda b=b: ops.residual_norm(res, bf, 1e-6, (x, None, None, 0.0), b.norm1.weight) for b in blocks])
+    out[f"{name}: residual sum + norm"] = bw(us, rows * w * (2 + 4 + 4 + 2))
+    seqs = (ctx.seq_slot, ctx.seq_q_start, ctx.seq_q_len)
+    n_seqs = ctx.n_seqs
+    pairs = [(b, e.cache) for b, e in zip(blocks, spec.schedule)]
+
+    # the delta rule
+    rec = [(b, e) for b, e in pairs if b.mixer.spec.kind == "gated_delta"]
+    m = rec[0][0].mixer
+    sp = m.spec
+    proj = rnd(rows, m.stacked.shape[0])
+    conv_state = n_seqs * (sp.conv - 1) * m.convolved * 4 * 2
+    us = in_graph([lambda b=b, e=e: ops.short_conv(proj, 0, m.convolved, b.mixer.conv, None, None, cache.entry_state(e), 0, *seqs,
+                                                    ctx.max_q_len, "silu") for b, e in rec])
+    out[f"{name}: short convolution + silu ({m.convolved} channels)"] = bw(us, rows * m.convolved * 4 + conv_state)
+    qkv = rnd(rows, m.convolved)
+    us = in_graph([lambda b=b, e=e: ops.state_scan("gated_delta", (qkv, 0), (qkv, m.qk), (qkv, 2 * m.qk),
+                                                    (proj, m.convolved + m.inner + sp.num_heads), (proj, m.convolved + m.inner),
+                                                    b.mixer.A_log, b.mixer.dt_bias, None, cache.entry_state(e),
+                                                    (sp.conv - 1) * m.convolved, *seqs, sp.num_heads, sp.num_kv_heads,
+                                                    sp.head_dim, sp.value_dim) for b, e in rec])
+    state_bytes = n_seqs * sp.num_heads * sp.head_dim * sp.value_dim * 4 * 2
+    d = bw(us, rows * (m.convolved * 2 + m.inner * 4) + state_bytes)
+    d["gflops"] = rows * sp.num_heads * sp.head_dim * sp.value_dim * 8 / us / 1e3
+    out[f"{name}: delta-rule recurrence (unit norms, state walk)"] = d
+    o32 = torch.randn(rows, m.inner, device=dev)
+    us = in_graph([lambda b=b: ops.group_norm_gate(o32, proj, m.convolved, b.mixer.gain, sp.num_heads, 1e-6, False, bf) for b, _ in rec])
+    out[f"{name}: head norm + gate"] = bw(us, rows * m.inner * (4 + 2 + 2))
+
+    # the recurrent unit
+    rec = [(b, e) for b, e in pairs if b.mixer.spec.kind == "gated_linear_recurrence"]
+    m = rec[0][0].mixer
+    sp = m.spec
+    c = sp.width
+    proj = rnd(rows, 2 * c)
+    u = rnd(rows, c)
+    us = in_graph([lambda b=b, e=e: ops.short_conv(proj, c, c, b.mixer.conv, b.mixer.conv_bias, b.mixer.x_bias, cache.entry_state(e), 0,
+                                                    *seqs, ctx.max_q_len) for b, e in rec])
+    out[f"{name}: short convolution ({c} channels)"] = bw(us, rows * c * 4 + n_seqs * (sp.conv - 1) * c * 8)
+    parts = u.view(rows, sp.blocks, m.block).transpose(0, 1)
+    us = in_graph([lambda b=b: torch.bmm(parts, b.mixer.gates, out_dtype=torch.float32) for b, _ in rec])
+    flops = rows * sp.blocks * m.block * 2 * m.block * 2
+    out[f"{name}: gate logits (library batched product)"] = tc(us, flops) if rows == prompt_len else bw(us, 2 * c * m.block * 2)
+    logits = torch.randn(sp.blocks, rows, 2 * m.block, device=dev)
+    us = in_graph([lambda b=b, e=e: ops.glru_scan(u, logits, b.mixer.ra_bias, b.mixer.ri_bias, b.mixer.lam, sp.decay_scale, proj, 0,
+                                                   b.mixer.y_bias, cache.entry_state(e), (sp.conv - 1) * c, *seqs, ctx.max_q_len)
+                   for b, e in rec])
+    out[f"{name}: gated linear recurrence (gates, decay, walk, gelu branch)"] = bw(us, rows * c * (2 + 8 + 2 + 2) + n_seqs * c * 8)
+
+    # window attention beside the state-space recurrence
+    par = [(b, e) for b, e in pairs if b.mixer.spec.kind == "parallel"]
+    m = par[0][0].mixer.sides["right"]
+    sp = m.spec
+    proj = rnd(rows, m.w_in.shape[0])
+    us = in_graph([lambda b=b, e=e: ops.short_conv(proj, m.inner, m.convolved, b.mixer.sides["right"].conv,
+                                                    b.mixer.sides["right"].conv_bias, None, cache.entry_state(e), 0, *seqs,
+                                                    ctx.max_q_len, "silu") for b, e in par])
+    out[f"{name}: short convolution + silu ({m.convolved} channels)"] = bw(us, rows * m.convolved * 4 + n_seqs * (sp.conv - 1) * m.convolved * 8)
+    xbc = rnd(rows, m.convolved)
+    us = in_graph([lambda b=b, e=e: ops.state_scan("state_space", (xbc, m.inner + m.bc), (xbc, m.inner), (xbc, 0),
+                                                    (proj, m.inner + m.convolved), None, b.mixer.sides["right"].A_log,
+                                                    b.mixer.sides["right"].dt_bias, b.mixer.sides["right"].D, cache.entry_state(e),
+                                                    (sp.conv - 1) * m.convolved, *seqs, sp.num_heads, sp.groups, sp.state,
+                                                    sp.head_dim) for b, e in par])
+    state_bytes = n_seqs * sp.num_heads * sp.state * sp.head_dim * 4 * 2
+    d = bw(us, rows * (m.convolved * 2 + m.inner * 4) + state_bytes)
+    d["gflops"] = rows * sp.num_heads * sp.state * sp.head_dim * 5 / us / 1e3
+    out[f"{name}: state-space recurrence (state walk)"] = d
+    o32 = torch.randn(rows, m.inner, device=dev)
+    us = in_graph([lambda b=b: ops.group_norm_gate(o32, proj, 0, b.mixer.sides["right"].gain, sp.norm_groups, 1e-6, True, bf)
+                   for b, _ in par])
+    out[f"{name}: gate + norm in groups"] = bw(us, rows * m.inner * (4 + 2 + 2))
+    a = par[0][0].mixer.sides["left"]
+    sp = a.spec
+    heads, kvh, dim = sp.num_heads, sp.num_kv_heads, sp.head_dim
+    proj = rnd(rows, a.qkvg.shape[0])
+    cos, sin, dims = ops.sink_tables(a.position.rotation(), dim)
+
+    def prepare(b, e):
+        k, v = cache.entry_pages(e)
+        ops.sink_prepare_rot(proj, heads, kvh, dim, dim, ctx.tok_pos, ctx.tok_slot, cache.block_table, k, v, cos, sin, dims,
+                             values_from_keys=True)
+
+    def attend(b, e):
+        k, v = cache.entry_pages(e)
+        return ops.sink_attention_step(proj, k, v, cache.block_table, ctx, heads, kvh, dim, dim, sp.scale, None,
+                                       b.mixer.sides["left"].sink, None, None, sp.window)
+
+    us = in_graph([lambda b=b, e=e: prepare(b, e) for b, e in par])
+    out[f"{name}: rotation of queries and keys, cache write"] = bw(us, rows * 2 * (2 * heads * dim + 3 * kvh * dim))
+    us = in_graph([lambda b=b, e=e: attend(b, e) for b, e in par])
+    if rows == prompt_len:
+        seen = sum(min(p + 1, sp.window) for p in range(prompt_len))
+        out[f"{name}: attention"] = tc(us, heads * 4 * dim * seen)
+    else:
+        out[f"{name}: attention"] = bw(us, batch * min(context + 1, sp.window) * 2 * kvh * dim * 2)
+    us = in_graph([lambda b=b: ops.norm_pair_mean(x, x, b.mixer.gains["left"], b.mixer.gains["right"], 1e-6) for b, _ in par])
+    out[f"{name}: two norms and their mean"] = bw(us, rows * w * 2 * 3)
+
+    # routed experts
+    routed = [b for b in blocks if getattr(b.feed_forward, "last_ids", "no") != "no"]
+    ff = routed[0].feed_forward
+    fs = ff.spec
+    ids, weights, gate = ops.moe_route_all(x, ff.router, ff.correction, fs.top, fs.group_count, fs.group_keep, shared_gate=True)
+    us = in_graph([lambda b=b: ops.moe_route_all(x, b.feed_forward.router, b.feed_forward.correction, fs.top, fs.group_count,
+                                                 fs.group_keep, shared_gate=True) for b in routed])
+    out[f"{name}: router"] = bw(us, rows * w * 2 + ff.router.shape[0] * w * 4)
+    shared = rnd(rows, w)
+    us = in_graph([lambda b=b: ops.moe_experts(x, ids, weights, b.feed_forward.gate_up, b.feed_forward.down, 0.0, "gated_silu",
+                                               identity=True, shared=shared, shared_gate=gate) for b in routed])
+    real = float((ids < fs.experts).float().mean())
+    flops = rows * fs.top * real * 3 * fs.intermediate_size * w * 2
+    if rows == prompt_len:
+        out[f"{name}: experts (gate, up, down, sum with identity and shared rows)"] = tc(us, flops)
+    else:
+        used = min(fs.experts, int(rows * fs.top * real) or 1)
+        out[f"{name}: experts (gate, up, down, sum with identity and shared rows)"] = bw(us, used * 3 * fs.intermediate_size * w * 2)
+    dense = [b for b in blocks if getattr(b.feed_forward.spec, "kind", "") == "dense_biased"]
+    us = in_graph([lambda b=b: b.feed_forward(x, None) for b in dense])
+    fd = dense[0].feed_forward.spec
+    if rows == prompt_len:
+        out[f"{name}: dense feed-forward (up, squared relu, down)"] = tc(us, rows * 2 * fd.intermediate_size * w * 2)
+    else:
+        out[f"{name}: dense feed-forward (up, squared relu, down)"] = bw(us, 2 * fd.intermediate_size * w * 2)
+
+
+def bavedra_compare(args) -> int:
+    """Beside Kesedra: the closest design this library has (a recurrence with a matrix state per head, attention
+    with a window, routed experts, a 32-bit residual stream)."""
+    return compare_with_qwen3(args, "bavedra", "Bavedra", bavedra_config, bavedra_kernels_alone, ["2048"],
+                              beside=("kesedra", "Kesedra", kesedra_config, kesedra_kernels_alone))
+
+
 def kesedra_compare(args) -> int:
     # the 2048 size alone by default: at 2560 with 8 layers a prompt step of this design failed to return while
     # its kernels still released their successors early; the larger sizes have not been timed since and run
@@ -746,11 +914,14 @@ def korurax_compare(args) -> int:
     return compare_with_qwen3(args, "korurax", "Korurax", korurax_config, korurax_kernels_alone, list(DESIGN_SIZES))
 
 
-def compare_with_qwen3(args, design_key, design_title, config_of, own_kernels, default_sizes) -> int:
-    """``--design kesedra`` / ``korurax``: prefill and decode throughput of that design beside Qwen3 (the closest
-    model this library has) at equal width, dense feed-forward, vocabulary and head count, and the design's own
-    kernels alone beside Qwen3's like kernels, each against its roofline.  Every number is timed on the device with
-    CUDA events; the kernels alone run inside a CUDA graph, once per layer.  Prints one JSON line."""
+def compare_with_qwen3(args, design_key, design_title, config_of, own_kernels, default_sizes, beside=None) -> int:
+    """``--design kesedra`` / ``korurax`` / ``bavedra``: prefill and decode throughput of that design beside Qwen3
+    (or, with ``beside = (key, title, config_of, kernels_alone)``, beside that design: the closest model this library
+    has) at equal width, dense feed-forward, vocabulary and head count, and the design's own kernels alone beside the
+    other's like kernels, each against its roofline.  Every number is timed on the device with CUDA events; the
+    kernels alone run inside a CUDA graph, once per layer.  Prints one JSON line."""
+    other_key, other_title, other_config, other_kernels = beside or ("qwen3", "Qwen3", qwen3_config, qwen3_kernels_alone)
+    kernels_of = {design_key: own_kernels, other_key: other_kernels}
     import torch
 
     from starter_b200 import ops
@@ -822,12 +993,8 @@ def compare_with_qwen3(args, design_key, design_title, config_of, own_kernels, d
                 ctx = runner.make_context([StepEntry(s, [1], []) for s in slots])
             x = rnd(rows, w)
             say(design, name, "kernels alone")
-            if design != "qwen3":
-                own_kernels(ops, out, name, rows, x, blocks, spec, cache, ctx, size, batch, context, prompt_len, rnd,
-                            in_graph, bw, tc)
-            else:
-                qwen3_kernels_alone(ops, out, name, rows, x, blocks, spec, cache, ctx, size, batch, context, prompt_len,
-                                    rnd, in_graph, bw, tc)
+            kernels_of[design](ops, out, name, rows, x, blocks, spec, cache, ctx, size, batch, context, prompt_len, rnd,
+                               in_graph, bw, tc)
             if rows == prompt_len:
                 runner.close_sequence(slot)
             else:
@@ -841,7 +1008,7 @@ def compare_with_qwen3(args, design_key, design_title, config_of, own_kernels, d
     for size_name in (args.design_sizes.split(",") if args.design_sizes else default_sizes):
         size = DESIGN_SIZES[size_name]
         row = {"layers": layers}
-        for design, raw in ((design_key, config_of(size, layers)), ("qwen3", qwen3_config(size, layers))):
+        for design, raw in ((design_key, config_of(size, layers)), (other_key, other_config(size, layers))):
             config = config_from_dict(raw)
             model = random_model(config, seed=0, dtype="bfloat16")
             vocab = model.spec.vocab_size
@@ -886,8 +1053,8 @@ def compare_with_qwen3(args, design_key, design_title, config_of, own_kernels, d
             torch.cuda.empty_cache()
         results[size_name] = row
     print(json.dumps({
-        "metric": "prefill tok/s at 2,048 tokens and decode tok/s at batch %d, context 2,048: %s beside Qwen3 at "
-                  "equal sizes (BF16, random weights)" % (batch, design_title),
+        "metric": "prefill tok/s at 2,048 tokens and decode tok/s at batch %d, context 2,048: %s beside %s at "
+                  "equal sizes (BF16, random weights)" % (batch, design_title, other_title),
         "unit": "tok/s", "n_gpus": 1, "dtype": "bf16", "steps": steps, "warmup": warmup,
         "data": "synthetic: random weights, uniform random token ids", "peaks": pk,
         "sizes": {k: DESIGN_SIZES[k] for k in results}, "results": results, "clocks": sampler.stop(windows)}))
@@ -911,9 +1078,9 @@ def main() -> int:
                              "generation range); the cache is sized for it")
     parser.add_argument("--per-stage", action="store_true",
                         help="also print where a decode step's time goes, kernel by kernel (stderr)")
-    parser.add_argument("--design", choices=["goguvik", "kesedra", "korurax"], default=None,
-                        help="instead of the default run: that design beside Qwen3 at equal sizes (prefill, decode, "
-                             "and each design's own kernels against their rooflines)")
+    parser.add_argument("--design", choices=["goguvik", "kesedra", "korurax", "bavedra"], default=None,
+                        help="instead of the default run: that design beside Qwen3 (Bavedra: beside Kesedra) at equal "
+                             "sizes (prefill, decode, and each design's own kernels against their rooflines)")
     parser.add_argument("--design-sizes", default=None, help="comma-separated subset of " + ",".join(DESIGN_SIZES))
     args = parser.parse_args()
     args.layers_given = "--layers" in sys.argv
@@ -926,6 +1093,8 @@ def main() -> int:
         return workload(args)
     if args.design == "korurax":
         return korurax_compare(args)
+    if args.design == "bavedra":
+        return bavedra_compare(args)
     if args.design == "kesedra":
         return kesedra_compare(args)
     if args.design:

@@ -12,8 +12,11 @@
 //
 // A block owns 32 columns of one head's S for one sequence: 256 threads = 32 columns x 8 lanes; lane p of a
 // column keeps rows p, p + 8, ... (KPT of them) in registers, and the eight lanes of a column sum S^T k and
-// S^T q by shuffles.  Tokens arrive in chunks of 16 through shared memory (q, k as floats, padded with zeros
-// to 8 * KPT rows; the unit norms are taken there, a warp a token), their outputs leave the same way.
+// S^T q by shuffles.  Both are taken from the state as the token finds it: with u the token's write,
+// (g S + k u^T)^T q = g S^T q + u (k . q), so one round of shuffles a token serves both and the decay is folded
+// into the write.  Tokens arrive in chunks of 16 through two shared-memory buffers (q, k as floats, padded with
+// zeros to 8 * KPT rows; k . q and the unit norms are taken there, a warp a token); the next chunk's global
+// loads are issued before the current chunk is walked and filed after it; outputs leave through shared memory.
 //
 // Also here: the RMS norm in equal parts of a row with a gate (group_norm_gate), and the mean of two rows each
 // RMS-normed with a gain of its own (norm_pair_mean).
@@ -32,6 +35,12 @@ __device__ __forceinline__ float sum8(float v) {
   return v;
 }
 
+// Shared memory of one buffer of SCAN_CT tokens: q and k as floats (NP entries a token), the block's 32 value
+// columns, and per token the decay, the factor (dt, or beta) and k . q.
+template <int NP> struct ScanBuffer {
+  float q[SCAN_CT][NP], k[SCAN_CT][NP], v[SCAN_CT][SCAN_COLS], dec[SCAN_CT], fac[SCAN_CT], kq[SCAN_CT];
+};
+
 template <typename T, int MODE, int KPT>
 __global__ void __launch_bounds__(256)
 state_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int ldk, const T* __restrict__ v, int ldv,
@@ -41,8 +50,10 @@ state_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int
                   const int* __restrict__ seq_slot, const int* __restrict__ seq_q_start,
                   const int* __restrict__ seq_q_len, int H, int G, int N, int V) {
   constexpr int NP = 8 * KPT;
-  __shared__ float qs[SCAN_CT][NP], ks[SCAN_CT][NP], vs[SCAN_CT][SCAN_COLS], os[SCAN_CT][SCAN_COLS];
-  __shared__ float dec[SCAN_CT], fac[SCAN_CT];
+  constexpr int QK_PER = (SCAN_CT * NP + 255) / 256, V_PER = SCAN_CT * SCAN_COLS / 256;
+  extern __shared__ __align__(16) unsigned char scan_smem[];
+  ScanBuffer<NP>* bufs = reinterpret_cast<ScanBuffer<NP>*>(scan_smem);
+  float (*os)[SCAN_COLS] = reinterpret_cast<float (*)[SCAN_COLS]>(scan_smem + 2 * sizeof(ScanBuffer<NP>));
   // (launch_dependents comes at this kernel's end, not its start: a long prompt keeps its blocks for a while)
   pdl_wait();
   SB_BEHIND_WAIT(q);
@@ -70,80 +81,119 @@ state_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int
   const float rate = expf(A_log[h]), bias = dt_bias[h], skip = (MODE == 0 && D) ? D[h] : 0.f;
   const float q_mult = MODE == 1 ? rsqrtf((float)N) : 1.f;
 
-  for (int t0 = 0; t0 < q_len; t0 += SCAN_CT) {
+  // a chunk's loads, held in registers while the chunk before is walked
+  T rq[QK_PER], rk[QK_PER], rv[V_PER];
+  float ra = 0.f, rb = 0.f;
+  auto fetch = [&](int t0) {
     const int ct = min(SCAN_CT, q_len - t0);
-    __syncthreads();                     // the chunk before has been read and its outputs stored
-    for (int e = tid; e < SCAN_CT * NP; e += 256) {
-      const int tt = e / NP, i = e - tt * NP;
+#pragma unroll
+    for (int n = 0; n < QK_PER; ++n) {
+      const int e = tid + 256 * n, tt = e / NP, i = e - tt * NP;
       const bool have = tt < ct && i < N;
-      const size_t row = (size_t)(q_start + t0 + tt);
-      qs[tt][i] = have ? to_f<T>(q[row * ldq + (size_t)g * N + i]) : 0.f;
-      ks[tt][i] = have ? to_f<T>(k[row * ldk + (size_t)g * N + i]) : 0.f;
+      const size_t row = (size_t)(q_start + t0 + (have ? tt : 0));
+      rq[n] = have ? q[row * ldq + (size_t)g * N + i] : from_f<T>(0.f);
+      rk[n] = have ? k[row * ldk + (size_t)g * N + i] : from_f<T>(0.f);
     }
-    for (int e = tid; e < SCAN_CT * SCAN_COLS; e += 256) {
-      const int tt = e / SCAN_COLS, c = e - tt * SCAN_COLS;
+#pragma unroll
+    for (int n = 0; n < V_PER; ++n) {
+      const int e = tid + 256 * n, tt = e / SCAN_COLS, c = e - tt * SCAN_COLS;
       const bool have = tt < ct && col0 + c < V;
-      vs[tt][c] = have ? to_f<T>(v[(size_t)(q_start + t0 + tt) * ldv + (size_t)h * V + col0 + c]) : 0.f;
+      rv[n] = have ? v[(size_t)(q_start + t0 + tt) * ldv + (size_t)h * V + col0 + c] : from_f<T>(0.f);
     }
     if (tid < ct) {
       const size_t row = (size_t)(q_start + t0 + tid);
-      const float dt = softplus_f(to_f<T>(a_raw[row * lda + h]) + bias);
-      dec[tid] = expf(-rate * dt);
-      fac[tid] = MODE == 0 ? dt : 1.f / (1.f + expf(-to_f<T>(b_raw[row * ldb + h])));
+      ra = to_f<T>(a_raw[row * lda + h]);
+      if (MODE == 1) rb = to_f<T>(b_raw[row * ldb + h]);
+    }
+  };
+  // the registers into a buffer, then (behind a barrier) per token k . q and, for the delta rule, the unit vectors
+  auto file = [&](ScanBuffer<NP>& b, int t0) {
+    const int ct = min(SCAN_CT, q_len - t0);
+#pragma unroll
+    for (int n = 0; n < QK_PER; ++n) {
+      const int e = tid + 256 * n;
+      if (e < SCAN_CT * NP) {
+        (&b.q[0][0])[e] = to_f<T>(rq[n]);
+        (&b.k[0][0])[e] = to_f<T>(rk[n]);
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < V_PER; ++n) (&b.v[0][0])[tid + 256 * n] = to_f<T>(rv[n]);
+    if (tid < ct) {
+      const float dt = softplus_f(ra + bias);
+      b.dec[tid] = expf(-rate * dt);
+      b.fac[tid] = MODE == 0 ? dt : 1.f / (1.f + expf(-rb));
     }
     __syncthreads();
-    if (MODE == 1) {
-      // unit vectors: a warp a token
-      for (int tt = warp; tt < ct; tt += 8) {
-        float sq = 0.f, sk = 0.f;
-        for (int i = lane; i < NP; i += 32) {
-          sq += qs[tt][i] * qs[tt][i];
-          sk += ks[tt][i] * ks[tt][i];
-        }
-        sq = warp_sum(sq);
-        sk = warp_sum(sk);
+    for (int tt = warp; tt < ct; tt += 8) {
+      float sq = 0.f, sk = 0.f, dot = 0.f;
+      for (int i = lane; i < NP; i += 32) {
+        const float a = b.q[tt][i], c = b.k[tt][i];
+        sq += a * a;
+        sk += c * c;
+        dot += a * c;
+      }
+      sq = warp_sum(sq);
+      sk = warp_sum(sk);
+      dot = warp_sum(dot);
+      if (MODE == 1) {
         const float mq = q_mult / sqrtf(sq + 1e-6f), mk = 1.f / sqrtf(sk + 1e-6f);
         for (int i = lane; i < NP; i += 32) {
-          qs[tt][i] *= mq;
-          ks[tt][i] *= mk;
+          b.q[tt][i] *= mq;
+          b.k[tt][i] *= mk;
         }
+        dot *= mq * mk;
       }
-      __syncthreads();
+      if (lane == 0) b.kq[tt] = dot;
     }
+    __syncthreads();
+  };
+
+  fetch(0);
+  file(bufs[0], 0);
+  int which = 0;
+  for (int t0 = 0; t0 < q_len; t0 += SCAN_CT, which ^= 1) {
+    const int ct = min(SCAN_CT, q_len - t0);
+    const bool more = t0 + SCAN_CT < q_len;
+    if (more) fetch(t0 + SCAN_CT);
+    const ScanBuffer<NP>& b = bufs[which];
     for (int tt = 0; tt < ct; ++tt) {
-      const float gd = dec[tt], x = vs[tt][jj];
-      float o = 0.f;
-      if (MODE == 1) {
-        float read = 0.f;
+      // both read-outs come from the state as the token finds it: with u the token's write,
+      // (g S + k u^T)^T q = g S^T q + u (k . q), so one round of shuffles a token serves both
+      const float gd = b.dec[tt], x = b.v[tt][jj];
+      float kk[KPT], r1a = 0.f, r1b = 0.f, r2a = 0.f, r2b = 0.f;
 #pragma unroll
-        for (int r = 0; r < KPT; ++r) {
-          S[r] *= gd;
-          read += S[r] * ks[tt][p + 8 * r];
+      for (int r = 0; r < KPT; ++r) {
+        kk[r] = b.k[tt][p + 8 * r];
+        const float qq = b.q[tt][p + 8 * r];
+        if (r & 1) {
+          if (MODE == 1) r1b += S[r] * kk[r];
+          r2b += S[r] * qq;
+        } else {
+          if (MODE == 1) r1a += S[r] * kk[r];
+          r2a += S[r] * qq;
         }
-        read = sum8(read);
-        const float u = fac[tt] * (x - read);
-#pragma unroll
-        for (int r = 0; r < KPT; ++r) {
-          S[r] += ks[tt][p + 8 * r] * u;
-          o += S[r] * qs[tt][p + 8 * r];
-        }
-        o = sum8(o);
-      } else {
-        const float u = fac[tt] * x;
-#pragma unroll
-        for (int r = 0; r < KPT; ++r) {
-          S[r] = gd * S[r] + ks[tt][p + 8 * r] * u;
-          o += S[r] * qs[tt][p + 8 * r];
-        }
-        o = sum8(o) + skip * x;
       }
-      if (p == 0) os[tt][jj] = o;
+      float r1 = r1a + r1b, r2 = r2a + r2b;
+      r2 = sum8(r2);
+      float u;
+      if (MODE == 1) {
+        r1 = sum8(r1);
+        u = b.fac[tt] * (x - gd * r1);
+      } else {
+        u = b.fac[tt] * x;
+      }
+#pragma unroll
+      for (int r = 0; r < KPT; ++r) S[r] = gd * S[r] + kk[r] * u;
+      if (p == 0) os[tt][jj] = gd * r2 + u * b.kq[tt] + skip * x;
     }
     __syncthreads();
     for (int e = tid; e < ct * SCAN_COLS; e += 256) {
       const int tt = e / SCAN_COLS, c = e - tt * SCAN_COLS;
       if (col0 + c < V) out[(size_t)(q_start + t0 + tt) * H * V + (size_t)h * V + col0 + c] = os[tt][c];
     }
+    if (more) file(bufs[which ^ 1], t0 + SCAN_CT);      // (its barriers also keep os until it is stored)
+    else __syncthreads();
   }
 #pragma unroll
   for (int r = 0; r < KPT; ++r) {
@@ -156,21 +206,24 @@ state_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int
 // A warp a (token, part).  order 0: y = rms(o * silu(z)) * w (the gate in front of the norm); order 1:
 // y = rms(o) * w * silu(z).  w has `wlen` entries and is read at (column mod wlen): a gain of the whole row,
 // or one of a part's size that every part shares.
-template <typename T>
+// WIDE: a block a (token, part) instead, for parts of many entries.
+template <typename T, bool WIDE>
 __global__ void group_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ z, int ldz,
                                        const float* __restrict__ w, int wlen, T* __restrict__ y, int n_tokens,
                                        int parts, int psize, float eps, int order) {
+  __shared__ float scratch[33];
   pdl_wait();      // no early launch_dependents: the successor starts when this kernel's blocks have exited
   SB_BEHIND_WAIT(o);
   SB_BEHIND_WAIT(z);
-  const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+  const long long item = WIDE ? (long long)blockIdx.x : ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = WIDE ? threadIdx.x : threadIdx.x & 31;
+  const int step = WIDE ? blockDim.x : 32;
   if (item >= (long long)n_tokens * parts) return;
   const int token = (int)(item / parts), part = (int)(item - (long long)token * parts);
   const float* orow = o + (size_t)token * parts * psize + (size_t)part * psize;
   const T* zrow = z + (size_t)token * ldz + (size_t)part * psize;
   float sq = 0.f;
-  for (int c = lane; c < psize; c += 32) {
+  for (int c = lane; c < psize; c += step) {
     float val = orow[c];
     if (order == 0) {
       const float gz = to_f<T>(zrow[c]);
@@ -178,10 +231,10 @@ __global__ void group_norm_gate_kernel(const float* __restrict__ o, const T* __r
     }
     sq += val * val;
   }
-  sq = warp_sum(sq);
+  sq = WIDE ? block_sum(sq, scratch) : warp_sum(sq);
   const float inv = 1.f / sqrtf(sq / (float)psize + eps);
   T* yrow = y + (size_t)token * parts * psize + (size_t)part * psize;
-  for (int c = lane; c < psize; c += 32) {
+  for (int c = lane; c < psize; c += step) {
     const float gz = to_f<T>(zrow[c]);
     const float silu = gz / (1.f + expf(-gz));
     const float gain = w[(part * psize + c) % wlen];
@@ -219,9 +272,14 @@ static int scan_launch(int kpt, dim3 grid, cudaStream_t s, const void* q, int ld
                        const float* dt_bias, const float* D, float* state, long long slot_stride, float* out,
                        const int* seq_slot, const int* seq_q_start, const int* seq_q_len, int H, int G, int N, int V) {
 #define SCAN_GO(KPT)                                                                                                   \
-  return launch_dependent(state_scan_kernel<T, MODE, KPT>, grid, dim3(256), 0, s, (const T*)q, ldq, (const T*)k, ldk,   \
-                          (const T*)v, ldv, (const T*)a_raw, lda, (const T*)b_raw, ldb, A_log, dt_bias, D, state,       \
-                          slot_stride, out, seq_slot, seq_q_start, seq_q_len, H, G, N, V)
+  {                                                                                                                    \
+    const size_t smem = 2 * sizeof(ScanBuffer<8 * KPT>) + SCAN_CT * SCAN_COLS * sizeof(float);                          \
+    if (smem > 48 * 1024)                                                                                              \
+      cudaFuncSetAttribute(state_scan_kernel<T, MODE, KPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+    return launch_dependent(state_scan_kernel<T, MODE, KPT>, grid, dim3(256), smem, s, (const T*)q, ldq, (const T*)k,   \
+                            ldk, (const T*)v, ldv, (const T*)a_raw, lda, (const T*)b_raw, ldb, A_log, dt_bias, D,       \
+                            state, slot_stride, out, seq_slot, seq_q_start, seq_q_len, H, G, N, V);                     \
+  }
   switch (kpt) {
     case 1: SCAN_GO(1);
     case 2: SCAN_GO(2);
@@ -264,12 +322,20 @@ int sb_group_norm_gate(int dtype, const float* o, const void* z, int ldz, const 
   if (n_tokens == 0) return 0;
   if (parts < 1 || psize < 1 || wlen < 1 || (order != 0 && order != 1)) return -2;
   const long long warps = (long long)n_tokens * parts;
+  if (psize > 256) {
+    const dim3 grid((unsigned)warps), block(psize >= 1024 ? 256 : 128);
+    if (dtype == 0)
+      return launch_dependent(group_norm_gate_kernel<float, true>, grid, block, 0, s, o, (const float*)z, ldz, w, wlen,
+                              (float*)y, n_tokens, parts, psize, eps, order);
+    return launch_dependent(group_norm_gate_kernel<bf16, true>, grid, block, 0, s, o, (const bf16*)z, ldz, w, wlen,
+                            (bf16*)y, n_tokens, parts, psize, eps, order);
+  }
   const dim3 grid((unsigned)((warps + 7) / 8));
   if (dtype == 0)
-    return launch_dependent(group_norm_gate_kernel<float>, grid, dim3(256), 0, s, o, (const float*)z, ldz, w, wlen,
+    return launch_dependent(group_norm_gate_kernel<float, false>, grid, dim3(256), 0, s, o, (const float*)z, ldz, w, wlen,
                             (float*)y, n_tokens, parts, psize, eps, order);
-  return launch_dependent(group_norm_gate_kernel<bf16>, grid, dim3(256), 0, s, o, (const bf16*)z, ldz, w, wlen, (bf16*)y,
-                          n_tokens, parts, psize, eps, order);
+  return launch_dependent(group_norm_gate_kernel<bf16, false>, grid, dim3(256), 0, s, o, (const bf16*)z, ldz, w, wlen,
+                          (bf16*)y, n_tokens, parts, psize, eps, order);
 }
 
 int sb_norm_pair_mean(int dtype, const void* a, const void* b, const float* wa, const float* wb, void* out, int n_tokens,
