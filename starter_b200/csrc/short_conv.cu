@@ -19,10 +19,12 @@
 // writes it at the end, so no block reads what another writes.  glru_scan: the recurrence is linear in S, so
 // a warp a segment of tokens first forms its segment's (product of a, sum) pair from a zero state, the
 // pairs are chained through shared memory, and each warp then walks its segment again from its true start.
+// Decays travel as their complements 1 - a (products of them as -expm1 of the summed logarithms).
 #include "common.cuh"
 
 #define CONV_MAX_TAPS 8
-#define CONV_CHUNK 64
+#define CONV_CHUNK 32
+#define CONV_BATCH 8      // tokens whose loads are in flight together
 
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -58,16 +60,24 @@ short_conv_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ ta
   }
   const float now = taps[(size_t)c * K + K - 1], b = bias ? bias[c] : 0.f;
   const int t1 = min(t0 + CONV_CHUNK, q_len);
-  for (int t = t0; t < t1; ++t) {
-    const float v = to_f<T>(x[(size_t)(q_start + t) * ldx + c]) + ib;
-    float a = b + now * v;
+  for (int tb = t0; tb < t1; tb += CONV_BATCH) {
+    float in[CONV_BATCH];
 #pragma unroll
-    for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) a += tap[j] * recent[j];
+    for (int i = 0; i < CONV_BATCH; ++i)
+      in[i] = tb + i < t1 ? to_f<T>(x[(size_t)(q_start + tb + i) * ldx + c]) + ib : 0.f;
 #pragma unroll
-    for (int j = CONV_MAX_TAPS - 2; j > 0; --j) recent[j] = recent[j - 1];
-    recent[0] = v;
-    if (act == 1) a = a / (1.f + expf(-a));
-    y[(size_t)(q_start + t) * ldy + c] = from_f<T>(a);
+    for (int i = 0; i < CONV_BATCH; ++i) {
+      if (tb + i >= t1) break;
+      const float v = in[i];
+      float a = b + now * v;
+#pragma unroll
+      for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) a += tap[j] * recent[j];
+#pragma unroll
+      for (int j = CONV_MAX_TAPS - 2; j > 0; --j) recent[j] = recent[j - 1];
+      recent[0] = v;
+      if (act == 1) a = a / (1.f + expf(-a));
+      y[(size_t)(q_start + tb + i) * ldy + c] = from_f<T>(a);
+    }
   }
   if (chunk != 0) return;
   // what the sequence's next step will find in front of it: its last K - 1 inputs, those of earlier
@@ -92,16 +102,18 @@ short_conv_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ ta
 
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-// One token of one channel: the decay a and what enters the state.
-template <typename T>
-__device__ __forceinline__ void glru_terms(const T* __restrict__ u, const float* __restrict__ zr,
-                                           const float* __restrict__ zi, size_t row, int ldu, int c, size_t gate_at,
-                                           float br, float bi, float rate, float& a, float& in) {
-  const float r = 1.f / (1.f + expf(-(zr[gate_at] + br)));
-  const float i = 1.f / (1.f + expf(-(zi[gate_at] + bi)));
-  const float log_a = -rate * r;                       // rate = c * softplus(lam)
-  a = expf(log_a);
-  in = sqrtf(-expm1f(2.f * log_a)) * i * to_f<T>(u[row * ldu + c]);
+#define GLRU_BATCH 8      // tokens whose loads are in flight together
+
+// One token of one channel: the decay's logarithm, its complement d = 1 - a and what enters the state, from its
+// gate logits and its input.  A decay close to one is kept as its complement: rounding a itself to a float would
+// lose up to 2^-24 / (1 - a) of the RATE of the decay, which is what a long memory is made of; S - d * S does not.
+__device__ __forceinline__ void glru_terms(float zr, float zi, float u, float br, float bi, float rate, float& log_a,
+                                           float& d, float& in) {
+  const float r = 1.f / (1.f + expf(-(zr + br)));
+  const float i = 1.f / (1.f + expf(-(zi + bi)));
+  log_a = -rate * r;                                   // rate = c * softplus(lam)
+  d = -expm1f(log_a);
+  in = sqrtf(-expm1f(2.f * log_a)) * i * u;
 }
 
 // Block = 32 channels (lanes) x `segments` warps; warp w walks tokens [w * per, (w + 1) * per) of its
@@ -139,29 +151,52 @@ glru_scan_kernel(const T* __restrict__ u, int ldu, const float* __restrict__ gat
   float* st = state + (size_t)seq_slot[seq] * slot_stride + cc;
   float S = 0.f;
   if (warps > 1) {
-    // the segment from a zero state: S_end = A * S_start + B
-    float A = 1.f, B = 0.f;
-    for (int t = t0; t < t1; ++t) {
-      float a, in;
-      glru_terms<T>(u, zr, zi, (size_t)(q_start + t), ldu, cc, (size_t)(q_start + t) * 2 * bs, br, bi, rate, a, in);
-      A *= a;
-      B = a * B + in;
+    // the segment from a zero state: S_end = A * S_start + B, with A kept as the sum of its logarithms
+    float A = 0.f, B = 0.f;
+    for (int tb = t0; tb < t1; tb += GLRU_BATCH) {
+      float vr[GLRU_BATCH], vi[GLRU_BATCH], vu[GLRU_BATCH];
+#pragma unroll
+      for (int n = 0; n < GLRU_BATCH; ++n) {
+        const size_t row = (size_t)(q_start + min(tb + n, t1 - 1));
+        vr[n] = zr[row * 2 * bs];
+        vi[n] = zi[row * 2 * bs];
+        vu[n] = to_f<T>(u[row * ldu + cc]);
+      }
+#pragma unroll
+      for (int n = 0; n < GLRU_BATCH; ++n) {
+        if (tb + n >= t1) break;
+        float log_a, d, in;
+        glru_terms(vr[n], vi[n], vu[n], br, bi, rate, log_a, d, in);
+        A += log_a;
+        B = fmaf(-d, B, B) + in;
+      }
     }
-    carry_a[warp][lane] = A;
+    carry_a[warp][lane] = -expm1f(A);
     carry_s[warp][lane] = B;
     __syncthreads();
     S = *st;
-    for (int w = 0; w < warp; ++w) S = carry_a[w][lane] * S + carry_s[w][lane];
+    for (int w = 0; w < warp; ++w) S = fmaf(-carry_a[w][lane], S, S) + carry_s[w][lane];
   } else {
     S = *st;
   }
-  for (int t = t0; t < t1; ++t) {
-    float a, in;
-    const size_t row = (size_t)(q_start + t);
-    glru_terms<T>(u, zr, zi, row, ldu, cc, row * 2 * bs, br, bi, rate, a, in);
-    S = a * S + in;
-    const float yv = to_f<T>(ybranch[row * ldy + cc]) + yb;
-    if (real) out[row * channels + c] = from_f<T>(S * gate_act(yv, SB_ACT_GELU_TANH));
+  for (int tb = t0; tb < t1; tb += GLRU_BATCH) {
+    float vr[GLRU_BATCH], vi[GLRU_BATCH], vu[GLRU_BATCH], vy[GLRU_BATCH];
+#pragma unroll
+    for (int n = 0; n < GLRU_BATCH; ++n) {
+      const size_t row = (size_t)(q_start + min(tb + n, t1 - 1));
+      vr[n] = zr[row * 2 * bs];
+      vi[n] = zi[row * 2 * bs];
+      vu[n] = to_f<T>(u[row * ldu + cc]);
+      vy[n] = to_f<T>(ybranch[row * ldy + cc]);
+    }
+#pragma unroll
+    for (int n = 0; n < GLRU_BATCH; ++n) {
+      if (tb + n >= t1) break;
+      float log_a, d, in;
+      glru_terms(vr[n], vi[n], vu[n], br, bi, rate, log_a, d, in);
+      S = fmaf(-d, S, S) + in;
+      if (real) out[(size_t)(q_start + tb + n) * channels + c] = from_f<T>(S * gate_act(vy[n] + yb, SB_ACT_GELU_TANH));
+    }
   }
   // the warp whose segment ends the sequence holds the state the next step starts from
   // (behind a barrier: every warp has read the old state by now)

@@ -38,7 +38,7 @@ __device__ __forceinline__ float sum8(float v) {
 // Shared memory of one buffer of SCAN_CT tokens: q and k as floats (NP entries a token), the block's 32 value
 // columns, and per token the decay, the factor (dt, or beta) and k . q.
 template <int NP> struct ScanBuffer {
-  float q[SCAN_CT][NP], k[SCAN_CT][NP], v[SCAN_CT][SCAN_COLS], dec[SCAN_CT], fac[SCAN_CT], kq[SCAN_CT];
+  float q[SCAN_CT][NP], k[SCAN_CT][NP], v[SCAN_CT][SCAN_COLS], dec[SCAN_CT], fac[SCAN_CT], kq[SCAN_CT];   // dec: 1 - decay
 };
 
 template <typename T, int MODE, int KPT>
@@ -121,7 +121,7 @@ state_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int
     for (int n = 0; n < V_PER; ++n) (&b.v[0][0])[tid + 256 * n] = to_f<T>(rv[n]);
     if (tid < ct) {
       const float dt = softplus_f(ra + bias);
-      b.dec[tid] = expf(-rate * dt);
+      b.dec[tid] = -expm1f(-rate * dt);        // the decay's complement 1 - g: see the walk
       b.fac[tid] = MODE == 0 ? dt : 1.f / (1.f + expf(-rb));
     }
     __syncthreads();
@@ -160,7 +160,9 @@ state_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int
     for (int tt = 0; tt < ct; ++tt) {
       // both read-outs come from the state as the token finds it: with u the token's write,
       // (g S + k u^T)^T q = g S^T q + u (k . q), so one round of shuffles a token serves both
-      const float gd = b.dec[tt], x = b.v[tt][jj];
+      // (the decay g arrives as d = 1 - g and is applied as S - d * S: a g close to one, rounded to a float,
+      // would lose up to 2^-24 / (1 - g) of the decay's rate)
+      const float dd = b.dec[tt], x = b.v[tt][jj];
       float kk[KPT], r1a = 0.f, r1b = 0.f, r2a = 0.f, r2b = 0.f;
 #pragma unroll
       for (int r = 0; r < KPT; ++r) {
@@ -179,13 +181,13 @@ state_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int
       float u;
       if (MODE == 1) {
         r1 = sum8(r1);
-        u = b.fac[tt] * (x - gd * r1);
+        u = b.fac[tt] * (x - fmaf(-dd, r1, r1));
       } else {
         u = b.fac[tt] * x;
       }
 #pragma unroll
-      for (int r = 0; r < KPT; ++r) S[r] = gd * S[r] + kk[r] * u;
-      if (p == 0) os[tt][jj] = gd * r2 + u * b.kq[tt] + skip * x;
+      for (int r = 0; r < KPT; ++r) S[r] = fmaf(kk[r], u, fmaf(-dd, S[r], S[r]));
+      if (p == 0) os[tt][jj] = fmaf(-dd, r2, r2) + u * b.kq[tt] + skip * x;
     }
     __syncthreads();
     for (int e = tid; e < ct * SCAN_COLS; e += 256) {
