@@ -12,7 +12,7 @@
 //
 // A block owns 32 columns of one head's S for one sequence: 256 threads = 32 columns x 8 lanes; lane p of a
 // column keeps rows p, p + 8, ... (KPT of them) in registers, and the eight lanes of a column sum S^T k and
-// S^T q by shuffles.  Both are taken from the state as the token finds it: with u the token's write,
+// S^T q by shuffles.  (States of more than 64 rows: 16 columns x 16 lanes.)  Both are taken from the state as the token finds it: with u the token's write,
 // (g S + k u^T)^T q = g S^T q + u (k . q), so one round of shuffles a token serves both and the decay is folded
 // into the write.  Tokens arrive in chunks of 16 through two shared-memory buffers (q, k as floats, padded with
 // zeros to 8 * KPT rows; k . q and the unit norms are taken there, a warp a token); the next chunk's global
@@ -23,25 +23,26 @@
 #include "common.cuh"
 
 #define SCAN_CT 16
-#define SCAN_COLS 32
 #define SCAN_MAX_N 256
 
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-__device__ __forceinline__ float sum8(float v) {
+// The sum over the P neighbouring lanes that share a column (P = 8 or 16).
+template <int P> __device__ __forceinline__ float sum_lanes(float v) {
   v += __shfl_xor_sync(0xffffffffu, v, 1);
   v += __shfl_xor_sync(0xffffffffu, v, 2);
   v += __shfl_xor_sync(0xffffffffu, v, 4);
+  if (P == 16) v += __shfl_xor_sync(0xffffffffu, v, 8);
   return v;
 }
 
 // Shared memory of one buffer of SCAN_CT tokens: q and k as floats (NP entries a token), the block's 32 value
 // columns, and per token the decay, the factor (dt, or beta) and k . q.
-template <int NP> struct ScanBuffer {
-  float q[SCAN_CT][NP], k[SCAN_CT][NP], v[SCAN_CT][SCAN_COLS], dec[SCAN_CT], fac[SCAN_CT], kq[SCAN_CT];   // dec: 1 - decay
+template <int NP, int COLS> struct ScanBuffer {
+  float q[SCAN_CT][NP], k[SCAN_CT][NP], v[SCAN_CT][COLS], dec[SCAN_CT], fac[SCAN_CT], kq[SCAN_CT];   // dec: 1 - decay
 };
 
-template <typename T, int MODE, int KPT>
+template <typename T, int MODE, int KPT, int P>
 __global__ void __launch_bounds__(256)
 state_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int ldk, const T* __restrict__ v, int ldv,
                   const T* __restrict__ a_raw, int lda, const T* __restrict__ b_raw, int ldb,
@@ -49,11 +50,12 @@ state_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int
                   float* __restrict__ state, long long slot_stride, float* __restrict__ out,
                   const int* __restrict__ seq_slot, const int* __restrict__ seq_q_start,
                   const int* __restrict__ seq_q_len, int H, int G, int N, int V) {
-  constexpr int NP = 8 * KPT;
+  constexpr int NP = P * KPT, SCAN_COLS = 256 / P;
   constexpr int QK_PER = (SCAN_CT * NP + 255) / 256, V_PER = SCAN_CT * SCAN_COLS / 256;
+  typedef ScanBuffer<NP, SCAN_COLS> Buffer;
   extern __shared__ __align__(16) unsigned char scan_smem[];
-  ScanBuffer<NP>* bufs = reinterpret_cast<ScanBuffer<NP>*>(scan_smem);
-  float (*os)[SCAN_COLS] = reinterpret_cast<float (*)[SCAN_COLS]>(scan_smem + 2 * sizeof(ScanBuffer<NP>));
+  Buffer* bufs = reinterpret_cast<Buffer*>(scan_smem);
+  float (*os)[SCAN_COLS] = reinterpret_cast<float (*)[SCAN_COLS]>(scan_smem + 2 * sizeof(Buffer));
   // (launch_dependents comes at this kernel's end, not its start: a long prompt keeps its blocks for a while)
   pdl_wait();
   SB_BEHIND_WAIT(q);
@@ -66,16 +68,16 @@ state_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int
   SB_BEHIND_WAIT(seq_q_start);
   SB_BEHIND_WAIT(seq_q_len);
   const int seq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * SCAN_COLS;
-  const int tid = threadIdx.x, p = tid & 7, jj = tid >> 3, lane = tid & 31, warp = tid >> 5;
-  const int j = col0 + jj;
-  const bool col = j < V;
+  const int tid = threadIdx.x, p = tid & (P - 1), jj = tid / P, lane = tid & 31, warp = tid >> 5;
   const int g = h / (H / G);
   const int q_start = seq_q_start[seq], q_len = seq_q_len[seq];
   float* sp = state + (size_t)seq_slot[seq] * slot_stride + (size_t)h * N * V;
+  const int j = col0 + jj;
+  const bool col = j < V;
   float S[KPT];
 #pragma unroll
   for (int r = 0; r < KPT; ++r) {
-    const int i = p + 8 * r;
+    const int i = p + P * r;
     S[r] = (col && i < N) ? sp[(size_t)i * V + j] : 0.f;
   }
   const float rate = expf(A_log[h]), bias = dt_bias[h], skip = (MODE == 0 && D) ? D[h] : 0.f;
@@ -107,7 +109,7 @@ state_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int
     }
   };
   // the registers into a buffer, then (behind a barrier) per token k . q and, for the delta rule, the unit vectors
-  auto file = [&](ScanBuffer<NP>& b, int t0) {
+  auto file = [&](Buffer& b, int t0) {
     const int ct = min(SCAN_CT, q_len - t0);
 #pragma unroll
     for (int n = 0; n < QK_PER; ++n) {
@@ -156,7 +158,7 @@ state_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int
     const int ct = min(SCAN_CT, q_len - t0);
     const bool more = t0 + SCAN_CT < q_len;
     if (more) fetch(t0 + SCAN_CT);
-    const ScanBuffer<NP>& b = bufs[which];
+    const Buffer& b = bufs[which];
     for (int tt = 0; tt < ct; ++tt) {
       // both read-outs come from the state as the token finds it: with u the token's write,
       // (g S + k u^T)^T q = g S^T q + u (k . q), so one round of shuffles a token serves both
@@ -166,8 +168,8 @@ state_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int
       float kk[KPT], r1a = 0.f, r1b = 0.f, r2a = 0.f, r2b = 0.f;
 #pragma unroll
       for (int r = 0; r < KPT; ++r) {
-        kk[r] = b.k[tt][p + 8 * r];
-        const float qq = b.q[tt][p + 8 * r];
+        kk[r] = b.k[tt][p + P * r];
+        const float qq = b.q[tt][p + P * r];
         if (r & 1) {
           if (MODE == 1) r1b += S[r] * kk[r];
           r2b += S[r] * qq;
@@ -177,10 +179,10 @@ state_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int
         }
       }
       float r1 = r1a + r1b, r2 = r2a + r2b;
-      r2 = sum8(r2);
+      r2 = sum_lanes<P>(r2);
       float u;
       if (MODE == 1) {
-        r1 = sum8(r1);
+        r1 = sum_lanes<P>(r1);
         u = b.fac[tt] * (x - fmaf(-dd, r1, r1));
       } else {
         u = b.fac[tt] * x;
@@ -199,7 +201,7 @@ state_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int
   }
 #pragma unroll
   for (int r = 0; r < KPT; ++r) {
-    const int i = p + 8 * r;
+    const int i = p + P * r;
     if (col && i < N) sp[(size_t)i * V + j] = S[r];
   }
 }
@@ -269,26 +271,30 @@ __global__ void norm_pair_mean_kernel(const T* __restrict__ a, const T* __restri
 }
 
 template <typename T, int MODE>
-static int scan_launch(int kpt, dim3 grid, cudaStream_t s, const void* q, int ldq, const void* k, int ldk, const void* v,
-                       int ldv, const void* a_raw, int lda, const void* b_raw, int ldb, const float* A_log,
+static int scan_launch(int kpt, int lanes, int n_seqs, cudaStream_t s, const void* q, int ldq, const void* k, int ldk,
+                       const void* v, int ldv, const void* a_raw, int lda, const void* b_raw, int ldb, const float* A_log,
                        const float* dt_bias, const float* D, float* state, long long slot_stride, float* out,
                        const int* seq_slot, const int* seq_q_start, const int* seq_q_len, int H, int G, int N, int V) {
-#define SCAN_GO(KPT)                                                                                                   \
+#define SCAN_GO(KPT, P)                                                                                                \
   {                                                                                                                    \
-    const size_t smem = 2 * sizeof(ScanBuffer<8 * KPT>) + SCAN_CT * SCAN_COLS * sizeof(float);                          \
+    const size_t smem = 2 * sizeof(ScanBuffer<P * KPT, 256 / P>) + SCAN_CT * (256 / P) * sizeof(float);                 \
     if (smem > 48 * 1024)                                                                                              \
-      cudaFuncSetAttribute(state_scan_kernel<T, MODE, KPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-    return launch_dependent(state_scan_kernel<T, MODE, KPT>, grid, dim3(256), smem, s, (const T*)q, ldq, (const T*)k,   \
-                            ldk, (const T*)v, ldv, (const T*)a_raw, lda, (const T*)b_raw, ldb, A_log, dt_bias, D,       \
-                            state, slot_stride, out, seq_slot, seq_q_start, seq_q_len, H, G, N, V);                     \
+      cudaFuncSetAttribute(state_scan_kernel<T, MODE, KPT, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    const dim3 grid(n_seqs, H, (V + 256 / P - 1) / (256 / P));                                                         \
+    return launch_dependent(state_scan_kernel<T, MODE, KPT, P>, grid, dim3(256), smem, s, (const T*)q, ldq,             \
+                            (const T*)k, ldk, (const T*)v, ldv, (const T*)a_raw, lda, (const T*)b_raw, ldb, A_log,      \
+                            dt_bias, D, state, slot_stride, out, seq_slot, seq_q_start, seq_q_len, H, G, N, V);         \
+  }
+  if (lanes == 16) {
+    if (kpt == 8) SCAN_GO(8, 16)
+    SCAN_GO(16, 16)
   }
   switch (kpt) {
-    case 1: SCAN_GO(1);
-    case 2: SCAN_GO(2);
-    case 4: SCAN_GO(4);
-    case 8: SCAN_GO(8);
-    case 16: SCAN_GO(16);
-    default: SCAN_GO(32);
+    case 1: SCAN_GO(1, 8)
+    case 2: SCAN_GO(2, 8)
+    case 4: SCAN_GO(4, 8)
+    case 8: SCAN_GO(8, 8)
+    default: SCAN_GO(16, 8)
   }
 #undef SCAN_GO
 }
@@ -307,10 +313,14 @@ int sb_state_scan(int dtype, int mode, const void* q, int ldq, const void* k, in
   if (n_seqs == 0) return 0;
   if (N < 1 || N > SCAN_MAX_N || V < 1 || H < 1 || G < 1 || H % G || (mode != 0 && mode != 1)) return -2;
   if (mode == 1 && !b_raw) return -2;
-  int kpt = 1;
-  while (8 * kpt < N) kpt *= 2;
-  const dim3 grid(n_seqs, H, (V + SCAN_COLS - 1) / SCAN_COLS);
-#define SCAN_ARGS kpt, grid, s, q, ldq, k, ldk, v, ldv, a_raw, lda, b_raw, ldb, A_log, dt_bias, D, state, slot_stride, out, \
+  // 8 lanes a column and 32 columns a block; for states of more than 64 rows in a step whose blocks would not
+  // fill the SMs twice (a prompt of one or two sequences), 16 lanes and 16 columns: half the rows a thread, twice
+  // the blocks, a shorter chain of sums a token
+  const long long blocks8 = (long long)n_seqs * H * ((V + 31) / 32);
+  const int lanes = N > 128 || (N > 64 && blocks8 < 2 * 148) ? 16 : 8;
+  int kpt = lanes == 16 ? 8 : 1;
+  while (lanes * kpt < N) kpt *= 2;
+#define SCAN_ARGS kpt, lanes, n_seqs, s, q, ldq, k, ldk, v, ldv, a_raw, lda, b_raw, ldb, A_log, dt_bias, D, state, slot_stride, out, \
                   seq_slot, seq_q_start, seq_q_len, H, G, N, V
   if (dtype == 0) return mode == 0 ? scan_launch<float, 0>(SCAN_ARGS) : scan_launch<float, 1>(SCAN_ARGS);
   return mode == 0 ? scan_launch<bf16, 0>(SCAN_ARGS) : scan_launch<bf16, 1>(SCAN_ARGS);
