@@ -103,7 +103,7 @@ class RoutedExperts(Part):
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
-        if spec.top > spec.experts:
+        if spec.top > spec.experts + getattr(spec, "identity_experts", 0):
             raise ValueError(f"{spec.top} choices among {spec.experts} experts")
         if spec.expert not in ops.MOE_EXPERTS or spec.scoring not in ops.MOE_SCORINGS:
             raise ValueError(f"no routed experts of kind {spec.expert!r} with scoring {spec.scoring!r}")

@@ -95,6 +95,15 @@ def test_what_is_refused(change, text):
         config_from_dict(raw)
 
 
+def test_more_choices_than_experts_when_identity_experts_make_up_for_it():
+    from starter_b200.engine.model import expected_tensors
+
+    raw = copy.deepcopy(B_B)
+    raw["layers"][3]["mlp"]["router"] = dict(experts=2, top=3, identity=2)
+    names = expected_tensors(spec_of(raw))
+    assert tuple(names["l3.mlp.router"].shape) == (4, 96) and "l3.mlp.e1.up" in names and "l3.mlp.e2.up" not in names
+
+
 def test_config_round_trip():
     from starter_b200.config import config_from_dict
 

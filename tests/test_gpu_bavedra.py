@@ -683,6 +683,69 @@ def test_unequal_batches_with_slots_pages_and_states_used_again(tmp_path_factory
     assert runner.cache.slots.held_count == 0 and runner.cache.pages.held_count == 0
 
 
+@pytest.mark.parametrize("seed", range(10))
+def test_configurations_drawn_at_random(tmp_path_factory, seed):
+    """Layer kinds, their order, every size, head count, window, tap count, group and constant drawn anew: three
+    unequal requests whole and alone, then begun together and decoded together, then one in portions, in float32
+    (the choice of experts itself is held) and, whole, in bfloat16 with the engine's choices handed over.  The
+    float32 bound is wider than elsewhere: some drawn models are ill-conditioned (the plain statement run in
+    float32 differs from itself in float64 by up to 7e-5 of the largest logit on them)."""
+    import random
+
+    from starter_b200.engine import ModelRunner, StepEntry, load_model
+    from tiny_bavedra import random_config
+
+    rng = random.Random(1000 + seed)
+    raw = random_config(rng)
+    folder = make_bavedra_folder(tmp_path_factory.mktemp(f"r{seed}"), f"R{seed}", seed=seed, dtype=torch.bfloat16, raw=raw)
+    cfg, w = plain.read_model_folder(folder)
+    lengths = [rng.choice([1, 3, 40, 130]), rng.choice([2, 70, 150]), rng.choice([5, 64, 65, 200])]
+    prompts = [random_prompt(n, cfg["vocab"], seed * 10 + i) for i, n in enumerate(lengths)]
+    want = [plain.forward(cfg, w, p) for p in prompts]
+    runner = ModelRunner(load_model(folder, "float32"), max_tokens=64 * 40, max_sequences=8, use_graphs=False)
+    for p, wanted in zip(prompts, want):
+        slot = runner.open_sequence()
+        got = runner.step([StepEntry(slot, p, all_places(len(p)))])
+        runner.close_sequence(slot)
+        close(got, wanted, "float32", f"whole, length {len(p)}", fp32=3e-4)
+    tails = [min(len(p) - 1, 20) for p in prompts]
+    heads = [len(p) - t for p, t in zip(prompts, tails)]
+    slots = [runner.open_sequence() for _ in prompts]
+    first = runner.step([StepEntry(s, p[:h], all_places(h)) for s, p, h in zip(slots, prompts, heads)])
+    got, at = [[] for _ in prompts], 0
+    for i, h in enumerate(heads):
+        got[i].append(first[at:at + h])
+        at += h
+    for step in range(max(tails)):
+        live = [i for i in range(3) if step < tails[i]]
+        out = runner.step([StepEntry(slots[i], [prompts[i][heads[i] + step]], [0]) for i in live])
+        for row, i in enumerate(live):
+            got[i].append(out[row:row + 1])
+    for i in range(3):
+        runner.close_sequence(slots[i])
+        close(torch.cat(got[i]), want[i], "float32", f"begun and decoded together, request {i}", fp32=3e-4)
+    slot, rows, at = runner.open_sequence(), [], 0
+    for n in (2, 1, 3, 61, 70, 200):
+        part = prompts[2][at:at + n]
+        if part:
+            rows.append(runner.step([StepEntry(slot, part, all_places(len(part)))]))
+            at += len(part)
+    runner.close_sequence(slot)
+    close(torch.cat(rows), want[2], "float32", "in portions", fp32=3e-4)
+    runner.check_status()
+    runner.cache.check()
+    assert runner.cache.slots.held_count == 0 and runner.cache.pages.held_count == 0
+    routed = Routed(ModelRunner(load_model(folder, "bfloat16"), max_tokens=64 * 40, max_sequences=8, use_graphs=False))
+    for p in prompts:
+        slot = routed.runner.open_sequence()
+        got = routed.step([StepEntry(slot, p, all_places(len(p)))], [len(p)])
+        routed.runner.close_sequence(slot)
+        held = plain.forward(cfg, w, p, routes=routed.routes(len(p), "bfloat16"))
+        # a drawn model may be ill-conditioned: the mean error says whether the mechanisms are right
+        mean = float((got.double().cpu() - held).abs().mean()) / float(held.abs().max())
+        assert mean <= 2e-2, f"bfloat16, length {len(p)}: mean error {mean:.3e} of the largest logit"
+
+
 @pytest.mark.parametrize("name", CONFIGS)
 def test_greedy_generation_through_the_entry_point(tmp_path_factory, name):
     """Unequal prompts through ``Engine.generate`` (the scheduler, the captured single-token step with its

@@ -80,7 +80,7 @@ B_B = dict(architecture="Bavedra", vocab=131, width=96, embedding=dict(scale=1.0
 # four query heads a key/value head and one, an attention without rotation; as many identity experts as experts;
 # state-space states of 64 and 128; a delta head of 128 x 64
 B_C = dict(architecture="Bavedra", vocab=257, width=128, embedding=dict(scale=11.0), norm=dict(eps=1e-5), layers=[
-    parallel(left(8, 2, 64, 0.125, 65, (10000.0, 32)), right(4, 32, 64, 2, 4, 2),
+    parallel(left(8, 2, 64, 0.11, 65, (10000.0, 32)), right(4, 32, 64, 2, 4, 2),
              moe(8, 2, 64, identity=8, groups=(4, 2), shared=64)),
     rglru(128, 2, 4, dense(192)),
     parallel(left(4, 4, 32, 0.18, 64), right(2, 64, 128, 1, 3, 4), None),
@@ -90,12 +90,64 @@ B_C = dict(architecture="Bavedra", vocab=257, width=128, embedding=dict(scale=11
 TINY_B = {"BA": B_A, "BB": B_B, "BC": B_C}
 
 
-def make_bavedra_folder(tmp_path, name, seed=0, dtype=torch.float32):
+def random_config(rng):
+    """A configuration drawn from ``rng`` (a ``random.Random``): two to six layers of any kind in any order, some
+    of them running an earlier layer's weights, with sizes, head counts, windows, taps, groups and constants drawn
+    anew for every layer."""
+    def feed_forward():
+        kind = rng.random()
+        if kind < 0.2:
+            return None
+        if kind < 0.45:
+            return dense(rng.choice([40, 64, 96, 136, 256]))
+        experts, identity = rng.choice([2, 3, 4, 6, 8, 12]), rng.choice([0, 0, 1, 2, 4])
+        outputs = experts + identity
+        count = rng.choice([c for c in (1, 2, 3, 4, 6) if outputs % c == 0])
+        keep = rng.randint(1, count)
+        top = rng.randint(1, min(outputs // count * keep, 4))
+        return moe(experts, top, rng.choice([16, 24, 32, 48, 64]), identity=identity if identity or rng.random() < 0.3 else None,
+                   groups=(count, keep) if count > 1 or rng.random() < 0.5 else None,
+                   shared=rng.choice([16, 40, 64, 96]) if rng.random() < 0.6 else None)
+
+    def layer():
+        kind = rng.choice(["rglru", "parallel", "delta"])
+        if kind == "rglru":
+            blocks = rng.choice([1, 2, 4])
+            return rglru(blocks * rng.choice([8, 16, 24, 32, 64]), blocks, rng.choice([2, 3, 4]), feed_forward())
+        if kind == "delta":
+            kv = rng.choice([1, 2, 4])
+            return delta(kv * rng.choice([1, 2]), kv, rng.choice([8, 16, 24, 32, 64, 128]), rng.choice([8, 16, 32, 48, 64]),
+                         rng.choice([2, 3, 4]), feed_forward())
+        kv, dim = rng.choice([1, 2, 4]), rng.choice([8, 16, 32, 64, 128])
+        attention = left(kv * rng.choice([1, 2, 4]), kv, dim, rng.choice([dim ** -0.5, 0.2, 0.1]),
+                         rng.choice([1, 2, 5, 17, 40, 64, 65, 100, 300]),
+                         (rng.choice([100.0, 1e4, 1e6]), rng.choice([d for d in (2, 4, 8, 16, 32, 64, 128) if d <= dim])))
+        groups = rng.choice([1, 2])
+        heads, vdim = groups * rng.choice([1, 2, 3]), rng.choice([8, 16, 24, 48, 64])
+        recurrence = right(heads, vdim, rng.choice([4, 16, 32, 48, 64, 128]), groups, rng.choice([2, 3, 4]),
+                           rng.choice([n for n in (1, 2, 3, 4) if (heads * vdim) % n == 0]))
+        return parallel(attention, recurrence, feed_forward())
+
+    layers = []
+    for _ in range(rng.randint(2, 6)):
+        own = [j for j, made in enumerate(layers) if "weights_of" not in made]
+        if own and rng.random() < 0.2:
+            source = rng.choice(own)
+            layers.append(again(layers[source], source))
+        else:
+            layers.append(layer())
+    return dict(architecture="Bavedra", vocab=rng.choice([97, 200, 333, 500, 1000]), width=rng.choice([48, 64, 72, 96, 128, 160, 256]),
+                embedding=dict(scale=rng.choice([1.0, 2.5, 4.0, 8.0])), norm=dict(eps=rng.choice([1e-6, 1e-5])), layers=layers)
+
+
+def make_bavedra_folder(tmp_path, name, seed=0, dtype=torch.float32, raw=None):
+    """A model folder of the tiny configuration ``name`` (or of ``raw``, a configuration given as it is)."""
     from starter_b200.config import config_from_dict
     from starter_b200.weights import write_model_folder
 
+    raw = TINY_B[name] if raw is None else raw
     path = os.path.join(str(tmp_path), f"tiny_{name}_{seed}")
-    write_model_folder(path, config_from_dict(TINY_B[name]), seed, dtype)
+    write_model_folder(path, config_from_dict(raw), seed, dtype)
     # The library draws matrices from N(0, 0.02): with those every score is near 0, every softmax near uniform,
     # every decay the same and every gate a half, and a wrong key, a lost state or a window that is one token off
     # would hardly show.  Larger matrices give scores of order one and routers that decide; decay constants spread
@@ -107,7 +159,7 @@ def make_bavedra_folder(tmp_path, name, seed=0, dtype=torch.float32):
     for key, value in tensors.items():
         v = value.float()
         if key == "embed":
-            v = v * (100.0 / TINY_B[name]["embedding"]["scale"])
+            v = v * (100.0 / raw["embedding"]["scale"])
         elif key.endswith((".left.q", ".left.k")):
             v = v * 14.0
         elif key.endswith(".router"):
