@@ -174,16 +174,17 @@ class BavedraConfig:
             _check_mixer(where + ".mixer", layer["type"], layer["mixer"])
             _check_mlp(where + ".mlp", layer.get("mlp"))
             source = layer.get("weights_of")
-            if source is not None:
-                if isinstance(source, bool) or not isinstance(source, int) or not 0 <= source < i:
-                    raise ConfigError(f"{where}.weights_of={source!r} must name an earlier layer")
-                other = checked[source]
-                if other.get("weights_of") is not None:
-                    raise ConfigError(f"{where}.weights_of={source}: that layer has no tensors of its own")
-                for key in ("type", "mixer", "mlp"):
-                    if other.get(key) != layer.get(key):
-                        raise ConfigError(f"{where}.weights_of={source}: its {key} differs from that layer's")
+            if source is not None and (isinstance(source, bool) or not isinstance(source, int)
+                                       or not 0 <= source < len(layers) or source == i):
+                raise ConfigError(f"{where}.weights_of={source!r} must name another layer of the model")
             checked.append(copy.deepcopy(dict(layer)))
+        for i, layer in enumerate(checked):
+            if layer.get("weights_of") is None:
+                continue
+            owner = cls._owner(checked, i)
+            for key in ("type", "mixer", "mlp"):
+                if checked[owner].get(key) != layer.get(key):
+                    raise ConfigError(f"layers[{i}].weights_of={layer['weights_of']}: its {key} differs from that layer's")
         return cls(
             vocab=_positive("vocab", raw["vocab"]),
             width=_positive("width", raw["width"]),
@@ -192,6 +193,18 @@ class BavedraConfig:
             layers=tuple(checked),
             torch_dtype=str(raw.get("torch_dtype", raw.get("dtype", "bfloat16"))),
         )
+
+    @staticmethod
+    def _owner(layers, i: int) -> int:
+        """The layer whose tensors layer ``i`` runs: itself, or what its ``weights_of`` leads to (a layer may name
+        one that comes later, or one that itself names another)."""
+        seen = set()
+        while layers[i].get("weights_of") is not None:
+            if i in seen:
+                raise ConfigError(f"layers[{i}].weights_of leads back to itself: no layer of that circle has tensors")
+            seen.add(i)
+            i = int(layers[i]["weights_of"])
+        return i
 
     # ------------------------------------------------------------------ writing
 
@@ -274,12 +287,9 @@ class BavedraConfig:
 
     def to_model_spec(self) -> ModelSpec:
         norm = NormSpec(size=self.width, eps=self.norm_eps, gain_32bit=True)
-        layers, schedule, place = [], [], {}
+        layers, place = [], {}
         for i, layer in enumerate(self.layers):
-            source = layer.get("weights_of")
-            if source is not None:
-                # the same parts once more, on a cache entry and state of this layer's own
-                schedule.append(ScheduleEntry(layer=place[int(source)], cache=i))
+            if layer.get("weights_of") is not None:
                 continue
             prefix = f"l{i}."
             mixer, names = self._mixer(layer["mixer"], layer["type"], prefix + "mix.")
@@ -294,7 +304,9 @@ class BavedraConfig:
                 spec = prenorm32_layer(mixer, None, norm, None, names)
             place[i] = len(layers)
             layers.append(spec)
-            schedule.append(ScheduleEntry(layer=place[i], cache=i))
+        # every layer of config.json is one run, on a cache entry and state of its own; a layer with
+        # ``weights_of`` is the same parts once more
+        schedule = [ScheduleEntry(layer=place[self._owner(self.layers, i)], cache=i) for i in range(len(self.layers))]
         ignored = tuple(f"l{i}.norm2" for i, layer in enumerate(self.layers)
                         if layer.get("mlp") is None and layer.get("weights_of") is None)
         return ModelSpec(

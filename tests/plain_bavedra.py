@@ -285,6 +285,13 @@ def mixer_of(layer, h, w, p, eps, positions):
     raise ValueError(layer["type"])
 
 
+def owner(layers, i):
+    """The layer whose tensors layer ``i`` runs: itself, or what its ``weights_of`` leads to."""
+    while layers[i].get("weights_of") is not None:
+        i = layers[i]["weights_of"]
+    return i
+
+
 def forward(cfg, w, tokens, layers_out=None, routes=None):
     """Logits ``[T, vocab]`` of one sequence from its first token; ``layers_out`` (a list) receives the
     residual stream after every layer; ``routes`` ({layer: ``[T, top]``}) fixes the experts of routed layers."""
@@ -292,7 +299,7 @@ def forward(cfg, w, tokens, layers_out=None, routes=None):
     positions = torch.arange(len(tokens))
     x = w["embed"][torch.as_tensor(tokens)] * cfg["embedding"]["scale"]
     for i, layer in enumerate(cfg["layers"]):
-        p = f"l{layer.get('weights_of', i)}."
+        p = f"l{owner(cfg['layers'], i)}."
         x = x + mixer_of(layer, norm(x, w[p + "norm1"], eps), w, p + "mix.", eps, positions)
         mlp = layer.get("mlp")
         if mlp is not None:

@@ -53,6 +53,19 @@ def test_run_order_of_layers_that_run_another_layers_weights():
     assert [(e.layer, e.cache) for e in order] == [(0, 0), (0, 1), (1, 2), (2, 3)]
 
 
+def test_a_layer_may_run_the_weights_of_a_later_layer_or_of_one_that_borrows_itself():
+    from starter_b200.engine.model import expected_tensors
+
+    raw = copy.deepcopy(B_A)
+    first = dict(raw["layers"][2], weights_of=3)            # in front of the layer that has the tensors
+    raw["layers"] = [first] + raw["layers"]                 # layers 1..5 are B_A's 0..4
+    raw["layers"][5]["weights_of"] = 0                      # 5 -> 0 -> 3
+    spec = spec_of(raw)
+    assert [(e.layer, e.cache) for e in spec.schedule] == [(2, 0), (0, 1), (1, 2), (2, 3), (3, 4), (2, 5)]
+    names = expected_tensors(spec)
+    assert "l3.mix.q" in names and not any(n.startswith(("l0.", "l5.")) for n in names)
+
+
 def test_tensor_names():
     from starter_b200.engine.model import expected_tensors
 
@@ -80,9 +93,10 @@ def test_tensor_names():
     (lambda c: c["layers"][1]["mlp"]["router"].update(top=5), "top"),
     (lambda c: c["layers"][1]["mlp"]["router"]["groups"].update(count=4), "groups"),
     (lambda c: c["layers"][1]["mlp"].update(kind="glu"), "feed-forwards"),
-    (lambda c: c["layers"][4].update(weights_of=4), "earlier"),
+    (lambda c: c["layers"][4].update(weights_of=4), "another layer"),
+    (lambda c: c["layers"][4].update(weights_of=7), "another layer"),
     (lambda c: c["layers"][4].update(weights_of=1), "differs"),
-    (lambda c: c["layers"].append(dict(c["layers"][4], weights_of=4)), "no tensors of its own"),
+    (lambda c: c["layers"][2].update(weights_of=4), "leads back to itself"),
     (lambda c: c.pop("norm"), "norm"),
     (lambda c: c.update(window=3), "window"),
 ])

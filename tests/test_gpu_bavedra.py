@@ -683,6 +683,27 @@ def test_unequal_batches_with_slots_pages_and_states_used_again(tmp_path_factory
     assert runner.cache.slots.held_count == 0 and runner.cache.pages.held_count == 0
 
 
+def test_a_layer_in_front_of_the_layer_whose_weights_it_runs(tmp_path_factory):
+    """``weights_of`` naming a later layer, and a layer that names one which itself borrows: each run has a state of
+    its own, whatever the order."""
+    import copy
+
+    from starter_b200.engine import ModelRunner, StepEntry, load_model
+
+    raw = copy.deepcopy(TINY_B["BA"])
+    raw["layers"] = [dict(raw["layers"][2], weights_of=3)] + raw["layers"]
+    raw["layers"][5]["weights_of"] = 0
+    folder = make_bavedra_folder(tmp_path_factory.mktemp("fw"), "FW", seed=3, raw=raw)
+    cfg, w = plain.read_model_folder(folder)
+    runner = ModelRunner(load_model(folder, "float32"), max_tokens=64 * 8, max_sequences=4, use_graphs=False)
+    prompt = random_prompt(70, cfg["vocab"], 4)
+    slot = runner.open_sequence()
+    got = [runner.step([StepEntry(slot, prompt[:50], all_places(50))])]
+    got += [runner.step([StepEntry(slot, [tok], [0])]) for tok in prompt[50:]]
+    runner.close_sequence(slot)
+    assert_close(torch.cat(got), plain.forward(cfg, w, prompt), "float32", "a borrowed layer in front")
+
+
 @pytest.mark.parametrize("seed", range(10))
 def test_configurations_drawn_at_random(tmp_path_factory, seed):
     """Layer kinds, their order, every size, head count, window, tap count, group and constant drawn anew: three
