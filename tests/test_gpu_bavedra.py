@@ -1,8 +1,6 @@
 """Bavedra on the GPU against the plain statement: each mechanism alone, then the model through the step
 function, the cache, the state slots and the generation loop, cut into steps and batches in every way."""
 
-import math
-
 import pytest
 import torch
 
@@ -367,8 +365,8 @@ def test_rotated_window_attention_with_a_sink_alone(heads, kv_heads, dim, rot, w
         first = max(q_pos - span + 1, 0)
         probes[q_pos] = first                           # the oldest key it still sees
         if first >= 1:
-            probes[q_pos - 1] = first - 1               # for the query before it, the same key lies just outside... its own oldest
-            probes[q_pos - 2] = first - 3 if first >= 3 else 0
+            probes[q_pos - 1] = first - 1               # the query before it: its own oldest key
+            probes[q_pos - 2] = first - 3 if first >= 3 else 0      # and one aimed at a key just behind its window
     probes[280], probes[191] = 280, max(128, 191 - span + 1)
     outside = {}
     for q_pos in (295, 260, 135):
